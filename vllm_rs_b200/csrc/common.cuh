@@ -203,7 +203,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 }
 // B200_MBAR_HINT_NS (compile time, experiment): suspend-time hint of try_wait.  Without a hint a waiting thread
 // comes back after ~20 cycles and re-polls: the single-lane producer / issuer warps of the decode GEMMs then
-// spend a measurable share of the SM's issue slots spinning (profiles/r2_c_dec_gemm_sass_histogram.txt).
+// spend a measurable share of the SM's issue slots spinning (profiles/r2_b_dec_gemm_diet_experiments.txt).
 #ifndef B200_MBAR_HINT_NS
 #define B200_MBAR_HINT_NS 0
 #endif

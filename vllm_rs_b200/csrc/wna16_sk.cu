@@ -3,7 +3,7 @@
 // Replaces marlin_*_4bit_f16 / gemm_half_q_half_alt for decode shapes (/root/reference/src/utils/gptq.rs:118-195,
 // wna16.rs:263-306).  Same data layout, epilogues and split meeting point as wna16_tc_dec.cu; what changes is how
 // the work is cut and who does what.  Motivation (round-2 measurements of the round-1 kernel,
-// profiles/r2_b_dec_gemm_diet_experiments.txt, r2_c_dec_gemm_sass_histogram.txt): two thirds of its issued
+// profiles/r2_b_dec_gemm_diet_experiments.txt): two thirds of its issued
 // instructions are pipeline bookkeeping, gate|up runs 1.51 waves, ~4 us of serial epilogue per launch.
 // Outcome (profiles/r2_j_sk_vs_dec.txt, ten measured iterations): bit-reproducible, the SAME weight arithmetic as
 // the reference and the round-1 kernel (w = fp16((q - z) * s), one rounding, before the MMA), parity green on every
@@ -35,7 +35,7 @@
 //     drain chain cost more than the multiplies it saved; ptxas re-derived the shared-memory base and the thread
 //     index from S2R at every barrier until both were pinned; a 32-row finaliser on two warps was the longest
 //     piece of the tail.
-//   * what still limits it (ncu source view): ~10 cycles per instruction per dequant warp with three dequant warps
+//   * what still limits it (ncu stall counters): ~10 cycles per instruction per dequant warp with three dequant warps
 //     per scheduler and a ~2 us dequant -> MMA chain per unit and group that small shapes cannot hide.
 #include <cstdlib>
 #include <cstring>

@@ -329,7 +329,7 @@ wna16_tc_dec_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     };
 #if B200_DEC_UNROLL
     {
-      // Ring-unrolled form of the loop below (round 2).  The ncu source view says the loop is bound by its serial
+      // Ring-unrolled form of the loop below (round 2).  The ncu stall counters say the loop is bound by its serial
       // bookkeeping, not by the dequant arithmetic (removing 60 % of the arithmetic bought 10 %): ring-stage indices,
       // barrier addresses, phase bits and TMEM columns recomputed per chunk with dependent ISETP / SEL / IMAD chains.
       // Unrolling by P = lcm(weight stages, A stages) chunks makes every one of them a compile-time constant of the
