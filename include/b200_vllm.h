@@ -662,6 +662,143 @@ int32_t b200_comm_world(const b200_comm*);
 void b200_runner_set_comm(b200_runner*, b200_comm*);
 void b200_runner_set_tp_fused(b200_runner*, int32_t on);
 
+
+/* ------------------------------------------------- hybrid decoders with an fp32 residual stream
+ * Decoders whose layers pick one of several sequence mixers -- latent (compressed-KV) attention with an optional
+ * sliding window and softmax sink, the gated delta rule, the SSD scan of Mamba-2 -- next to a routed mixture of
+ * experts with a shared expert, both reading ONE norm of the stream (parallel layer).  Residual, norms, softmax,
+ * router and recurrent state are fp32; `dt` picks the dtype of every matrix-product operand and of the latent cache
+ * (0 = bf16, 1 = fp32, true fp32 products).  A step is a ragged batch: sequence b brings rows [cu[b], cu[b+1]) that
+ * end at position context_lens[b] - 1, so prompt portions of any length and single decoded tokens mix freely.
+ * Kernels: csrc/seq_norms.cu, latent_attn.cu, linear_recurrence.cu, moe.cu; launch plan: csrc/host/hybrid_runner.cpp. */
+#define B200_MIXER_LATENT_ATTN 0
+#define B200_MIXER_DELTA_RULE 1
+#define B200_MIXER_SSD 2
+
+void b200_resid_rmsnorm(void* out, const float* x, const float* w, int32_t num_tokens, int32_t width, float eps,
+                        float w_offset, int32_t dt, int64_t stream);
+void b200_gated_group_norm(void* out, const float* y, int32_t ldy, const float* gate, int32_t ldg, const float* w,
+                           int32_t w_period, int32_t num_tokens, int32_t channels, int32_t group, float eps,
+                           int32_t gate_first, int32_t dt, int64_t stream);
+/* qc fp32 [T, ldq] = [q (heads x (dim + rot_dim)) | latent (kv_rank) | shared rotated key (rot_dim)] -> cache row at
+ * slot_mapping[t] ([normed latent | rotated key], dtype dt), q_plain [T, heads, dim] (dtype dt) and the rotated query
+ * parts in q_full [T, heads, kv_rank + rot_dim] fp32 (entries kv_rank.. of every head).  rot_freq f64 [rot_dims / 2]. */
+void b200_latent_prep(const float* qc, int32_t ldq, void* q_plain, float* q_full, void* cache,
+                      const float* latent_norm_w, const double* rot_freq, float rot_mag, const int64_t* positions,
+                      const int64_t* slot_mapping, int32_t num_tokens, int32_t heads, int32_t dim, int32_t rot_dim,
+                      int32_t rot_dims, int32_t kv_rank, float eps, int32_t dt, int64_t stream);
+/* out [T, heads, kv_rank] (dtype dt) = softmax-weighted sum of cached latents; sink fp32 [heads] or NULL;
+ * window <= 0: full causal context.  cache [num_blocks, 64, kv_rank + rot_dim].                                   */
+void b200_latent_attn(void* out, const float* q_full, const void* cache, const float* sink,
+                      const uint32_t* cu_seqlens_q, const uint32_t* context_lens, const uint32_t* block_tables,
+                      int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens, int32_t heads, int32_t kv_rank,
+                      int32_t rot_dim, int32_t window, float scale, int32_t dt, int64_t stream);
+/* Causal per-channel convolution + SiLU; state fp32 [slots, taps - 1, channels]; taps_w fp32 [channels, taps] (last
+ * column = current token), bias fp32 [channels] or NULL.  out may alias x.                                        */
+void b200_short_conv_silu(float* out, int32_t ldo, const float* x, int32_t ldx, const float* taps_w, const float* bias,
+                          float* state, const int32_t* state_slots, const uint32_t* cu_seqlens_q,
+                          const uint32_t* context_lens, int32_t num_seqs, int32_t channels, int32_t taps,
+                          int64_t stream);
+/* q, k [T, kv_heads, dim], v [T, heads, vdim] (row stride ld), b_raw / a_raw [T, heads] (row stride ld_ba), all fp32;
+ * out fp32 [T, heads, vdim]; state fp32 [slots, heads, dim, vdim].                                                 */
+void b200_delta_rule(float* out, const float* q, const float* k, const float* v, int32_t ld, const float* b_raw,
+                     const float* a_raw, int32_t ld_ba, const float* a_log, const float* dt_bias, float* state,
+                     const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                     int32_t num_seqs, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int64_t stream);
+/* x [T, heads, vdim], Bm / Cm [T, groups, nstate] (row stride ld), dt_raw [T, heads] (row stride ld_dt), fp32;
+ * out fp32 [T, heads, vdim]; state fp32 [slots, heads, nstate, vdim]; d_skip may be NULL.                          */
+void b200_ssd_scan(float* out, const float* x, const float* Bm, const float* Cm, int32_t ld, const float* dt_raw,
+                   int32_t ld_dt, const float* a_log, const float* dt_bias, const float* d_skip, float* state,
+                   const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                   int32_t num_seqs, int32_t heads, int32_t groups, int32_t nstate, int32_t vdim, int64_t stream);
+void b200_moe_route(const float* logits, int32_t num_tokens, int32_t experts, int32_t top, float scale,
+                    int32_t* top_idx, float* top_w, int64_t stream);
+int64_t b200_moe_workspace_bytes(int32_t num_tokens, int32_t experts, int32_t top, int32_t width, int32_t ff);
+/* x fp32 [T, width] += sum over a token's choices of top_w * expert(h); w_gate_up [E, 2 ff, width] (gate rows first),
+ * w_down [E, width, ff], h [T, width], all dtype dt.                                                               */
+void b200_moe_experts(float* x, const void* h, const int32_t* top_idx, const float* top_w, const void* w_gate_up,
+                      const void* w_down, int32_t num_tokens, int32_t experts, int32_t top, int32_t width, int32_t ff,
+                      int32_t dt, void* workspace, int64_t stream);
+
+typedef struct b200_hybrid_config {
+  int32_t width, vocab, num_layers;
+  int32_t dt;                               /* 0 = bf16 operands and cache, 1 = fp32 */
+  int32_t block_size, num_blocks, max_blocks_per_seq;
+  int32_t max_seqs, max_tokens;             /* per step */
+  int32_t num_state_slots;
+  float norm_eps, norm_weight_offset;       /* layer / final norms multiply by (offset + w) */
+} b200_hybrid_config;
+
+typedef struct b200_hybrid_layer {
+  int32_t mixer;                            /* B200_MIXER_* */
+  int32_t heads, kv_heads;                  /* kv_heads: q / k heads of the delta rule, B / C groups of the SSD scan */
+  int32_t dim, rot_dim, rot_dims, vdim, kv_rank, window;
+  int32_t state, conv_taps, norm_groups;
+  float scale, rot_mag;
+  int32_t experts, top, expert_ff, shared_ff;   /* experts == 0: no routed experts; shared_ff == 0: no shared expert */
+  float route_scale;
+  const void* norm_w;                       /* fp32 [width] */
+  /* matrix-product weights, dtype dt, rows = outputs.  w_in fuses the mixer's input projections:
+   *   latent attention: [q: heads x (dim + rot_dim) | latent: kv_rank | rotated key: rot_dim]
+   *   delta rule:       [q: kv_heads x dim | k: kv_heads x dim | v: heads x vdim | b: heads | a: heads | gate: heads x vdim]
+   *   SSD:              [z: heads x vdim | x: heads x vdim | B: groups x state | C: groups x state | dt: heads]      */
+  const void *w_in, *w_uk, *w_uv, *w_o;
+  /* small fp32 parameters */
+  const void *latent_norm_w, *sink, *conv_w, *conv_b, *a_log, *dt_bias, *d_skip, *out_norm_w;
+  const double* rot_freq;                   /* f64 [rot_dims / 2], device */
+  const void *w_router, *w_gate_up, *w_down, *w_shared_gate_up, *w_shared_down;
+  void *kv_cache, *conv_state, *rec_state;  /* caller-owned pools (see the kernels above for their shapes) */
+} b200_hybrid_layer;
+
+typedef struct b200_hybrid b200_hybrid;
+b200_hybrid* b200_hybrid_new(const b200_hybrid_config* cfg);
+void b200_hybrid_free(b200_hybrid*);
+void b200_hybrid_set_layer(b200_hybrid*, int32_t layer, const b200_hybrid_layer* l);
+/* embed [vocab, width], lm_head [vocab, width] in dtype dt; final_norm fp32 [width] */
+void b200_hybrid_set_globals(b200_hybrid*, const void* embed, const void* final_norm, const void* lm_head);
+int64_t b200_hybrid_workspace_bytes(const b200_hybrid*);
+void b200_hybrid_set_workspace(b200_hybrid*, void* workspace, int64_t bytes);
+/* fp32 [num_layers, max_tokens, width] device buffer that receives the residual stream after every layer (NULL: off) */
+void b200_hybrid_set_layer_trace(b200_hybrid*, float* buf);
+/* One step from DEVICE inputs.  out_rows u32 [num_out]: token rows whose logits are wanted (a sequence's last row
+ * when generating); logits fp32 [num_out, vocab] and / or out_ids u32 [num_out] (either may be NULL) are written;
+ * sampling as set by b200_hybrid_set_sampling (default greedy).                                                    */
+void b200_hybrid_step(b200_hybrid*, const uint32_t* input_ids, const int64_t* positions, const int64_t* slot_mapping,
+                      const uint32_t* cu_seqlens_q, const uint32_t* context_lens, const uint32_t* block_tables,
+                      const int32_t* state_slots, const uint32_t* out_rows, int32_t num_seqs, int32_t num_tokens,
+                      int32_t max_blocks, int32_t num_out, float* logits, uint32_t* out_ids, int64_t stream);
+/* The same from HOST (pinned) inputs: H2D of the step's inputs, the step, D2H of ids and / or logits, stream sync. */
+int32_t b200_hybrid_step_host(b200_hybrid*, const uint32_t* input_ids, const int64_t* positions,
+                              const int64_t* slot_mapping, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                              const uint32_t* block_tables, const int32_t* state_slots, const uint32_t* out_rows,
+                              int32_t num_seqs, int32_t num_tokens, int32_t max_blocks, int32_t num_out,
+                              float* logits_host, uint32_t* out_ids_host, int64_t stream);
+int32_t b200_hybrid_set_sampling(b200_hybrid*, int32_t strategy, int32_t k, float p, float t);
+void b200_hybrid_set_step_seed(b200_hybrid*, uint64_t seed, int64_t stream);
+int64_t b200_hybrid_launches_per_step(const b200_hybrid*);
+
+/* ------------------------------------------------- state slots and host-driven steps of the scheduler
+ * Models with recurrent state give every running sequence one slot of `n` (enable_state_slots): schedule() admits a
+ * waiting sequence only while a slot is free, finished / swapped-out sequences give theirs back.  A STREAMED sequence
+ * is driven by the host instead of schedule(): open (takes a slot when slots are enabled), feed tokens (its block
+ * table grows by whole blocks as needed), run them with b200_prepare_ragged, close (blocks and slot return).
+ * b200_prepare_ragged builds the step metadata of ANY mix of running sequences.  mode 0 (a scheduled prefill chunk):
+ * sequence i brings tokens [num_cached_tokens, + counts[i]) (counts NULL: min(chunk_size, the rest)); mode 1 (decode):
+ * its last counts[i] tokens (NULL: 1); mode 2 (streamed): as mode 0 with counts NULL = everything fed since the last
+ * step, and num_cached_tokens advances.  block_tables is [n, max_blocks_cap], zero padded.  Returns the number of
+ * token rows, -1 when a capacity is too small, -2 for a bad index / count.                                           */
+int32_t b200_scheduler_enable_state_slots(b200_scheduler*, int32_t n);
+int32_t b200_scheduler_num_free_state_slots(const b200_scheduler*);
+int32_t b200_scheduler_seq_state_slot(const b200_scheduler*, int32_t running_idx);
+int64_t b200_scheduler_open(b200_scheduler*);
+int32_t b200_scheduler_feed(b200_scheduler*, int64_t seq_id, const uint32_t* tokens, int32_t n);
+int32_t b200_scheduler_close(b200_scheduler*, int64_t seq_id);
+int32_t b200_scheduler_running_index(const b200_scheduler*, int64_t seq_id);
+int32_t b200_prepare_ragged(b200_scheduler*, const int32_t* indices, const int32_t* counts, int32_t n, int32_t mode,
+                            int32_t token_cap, int32_t max_blocks_cap, uint32_t* input_ids,
+                            int64_t* positions, int64_t* slot_mapping, uint32_t* cu_seqlens_q, uint32_t* context_lens,
+                            uint32_t* block_tables, int32_t* state_slots);
+
 #ifdef __cplusplus
 }
 #endif

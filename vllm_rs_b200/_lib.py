@@ -13,6 +13,8 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 # B200_LIB_PATH: load an instrumented build instead (tools/dec_trace.py builds one with -DB200_DEC_TRACE)
 LIB_PATH = Path(os.environ["B200_LIB_PATH"]) if os.environ.get("B200_LIB_PATH") else PKG / "libb200_vllm.so"
+# the subset library of the fp32-residual hybrid decoders (build.py --target hybrid): loaded when the full one is absent
+HYBRID_LIB_PATH = PKG / "libb200_hybrid.so"
 HEADER = PKG.parent / "include" / "b200_vllm.h"
 
 _lib = None
@@ -42,6 +44,27 @@ class LayerWeights(C.Structure):
         "gate_up_w", "gate_up_s", "gate_up_z",
         "down_w", "down_s", "down_z",
         "k_cache", "v_cache")]
+
+
+class HybridConfig(C.Structure):
+    """b200_hybrid_config (include/b200_vllm.h)."""
+
+    _fields_ = [(n, c_i32) for n in ("width", "vocab", "num_layers", "dt", "block_size", "num_blocks",
+                                     "max_blocks_per_seq", "max_seqs", "max_tokens", "num_state_slots")] + \
+               [("norm_eps", c_f32), ("norm_weight_offset", c_f32)]
+
+
+class HybridLayer(C.Structure):
+    """b200_hybrid_layer (include/b200_vllm.h)."""
+
+    _fields_ = [(n, c_i32) for n in ("mixer", "heads", "kv_heads", "dim", "rot_dim", "rot_dims", "vdim", "kv_rank",
+                                     "window", "state", "conv_taps", "norm_groups")] + \
+               [("scale", c_f32), ("rot_mag", c_f32)] + \
+               [(n, c_i32) for n in ("experts", "top", "expert_ff", "shared_ff")] + [("route_scale", c_f32)] + \
+               [(n, c_vp) for n in ("norm_w", "w_in", "w_uk", "w_uv", "w_o", "latent_norm_w", "sink", "conv_w", "conv_b",
+                                    "a_log", "dt_bias", "d_skip", "out_norm_w", "rot_freq", "w_router", "w_gate_up",
+                                    "w_down", "w_shared_gate_up", "w_shared_down", "kv_cache", "conv_state",
+                                    "rec_state")]
 
 
 class KvCachePlan(C.Structure):
@@ -209,6 +232,37 @@ _SIGS = {
     "b200_allreduce_f16": (None, [c_vp, c_vp, c_i64, c_i64]),
     "b200_comm_rank": (c_i32, [c_vp]),
     "b200_comm_world": (c_i32, [c_vp]),
+    # hybrid decoders with an fp32 residual stream
+    "b200_resid_rmsnorm": (None, [c_vp] * 3 + [c_i32, c_i32, c_f32, c_f32, c_i32, c_i64]),
+    "b200_gated_group_norm": (None, [c_vp, c_vp, c_i32, c_vp, c_i32, c_vp] + [c_i32] * 4 + [c_f32, c_i32, c_i32, c_i64]),
+    "b200_latent_prep": (None, [c_vp, c_i32] + [c_vp] * 5 + [c_f32, c_vp, c_vp] + [c_i32] * 6 + [c_f32, c_i32, c_i64]),
+    "b200_latent_attn": (None, [c_vp] * 7 + [c_i32] * 7 + [c_f32, c_i32, c_i64]),
+    "b200_short_conv_silu": (None, [c_vp, c_i32, c_vp, c_i32] + [c_vp] * 6 + [c_i32] * 3 + [c_i64]),
+    "b200_delta_rule": (None, [c_vp] * 4 + [c_i32, c_vp, c_vp, c_i32] + [c_vp] * 6 + [c_i32] * 5 + [c_i64]),
+    "b200_ssd_scan": (None, [c_vp] * 4 + [c_i32, c_vp, c_i32] + [c_vp] * 7 + [c_i32] * 5 + [c_i64]),
+    "b200_moe_route": (None, [c_vp, c_i32, c_i32, c_i32, c_f32, c_vp, c_vp, c_i64]),
+    "b200_moe_workspace_bytes": (c_i64, [c_i32] * 5),
+    "b200_moe_experts": (None, [c_vp] * 6 + [c_i32] * 6 + [c_vp, c_i64]),
+    "b200_hybrid_new": (c_vp, [C.POINTER(HybridConfig)]),
+    "b200_hybrid_free": (None, [c_vp]),
+    "b200_hybrid_set_layer": (None, [c_vp, c_i32, C.POINTER(HybridLayer)]),
+    "b200_hybrid_set_globals": (None, [c_vp] * 4),
+    "b200_hybrid_workspace_bytes": (c_i64, [c_vp]),
+    "b200_hybrid_set_workspace": (None, [c_vp, c_vp, c_i64]),
+    "b200_hybrid_set_layer_trace": (None, [c_vp, c_vp]),
+    "b200_hybrid_step": (None, [c_vp] * 9 + [c_i32] * 4 + [c_vp, c_vp, c_i64]),
+    "b200_hybrid_step_host": (c_i32, [c_vp] * 9 + [c_i32] * 4 + [c_vp, c_vp, c_i64]),
+    "b200_hybrid_set_sampling": (c_i32, [c_vp, c_i32, c_i32, c_f32, c_f32]),
+    "b200_hybrid_set_step_seed": (None, [c_vp, C.c_uint64, c_i64]),
+    "b200_hybrid_launches_per_step": (c_i64, [c_vp]),
+    "b200_scheduler_enable_state_slots": (c_i32, [c_vp, c_i32]),
+    "b200_scheduler_num_free_state_slots": (c_i32, [c_vp]),
+    "b200_scheduler_seq_state_slot": (c_i32, [c_vp, c_i32]),
+    "b200_scheduler_open": (c_i64, [c_vp]),
+    "b200_scheduler_feed": (c_i32, [c_vp, c_i64, c_vp, c_i32]),
+    "b200_scheduler_close": (c_i32, [c_vp, c_i64]),
+    "b200_scheduler_running_index": (c_i32, [c_vp, c_i64]),
+    "b200_prepare_ragged": (c_i32, [c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32] + [c_vp] * 7),
 }
 
 
@@ -222,11 +276,16 @@ def declared_symbols() -> list[str]:
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
-        if not LIB_PATH.exists():
+        path, subset = LIB_PATH, False
+        if not path.exists() and HYBRID_LIB_PATH.exists() and not os.environ.get("B200_LIB_PATH"):
+            path, subset = HYBRID_LIB_PATH, True
+        if not path.exists():
             raise RuntimeError(
                 f"{LIB_PATH} is missing: run `python -m vllm_rs_b200.build` (there is no CPU fallback)")
-        _lib = C.CDLL(str(LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else 0)
+        _lib = C.CDLL(str(path), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else 0)
         for name, (res, args) in _SIGS.items():
+            if subset and not hasattr(_lib, name):
+                continue                  # a symbol of the full library: using it raises AttributeError
             fn = getattr(_lib, name)
             fn.restype = res
             fn.argtypes = args

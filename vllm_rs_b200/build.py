@@ -2,8 +2,11 @@
 
     python -m vllm_rs_b200.build          # incremental
     python -m vllm_rs_b200.build --force
+    python -m vllm_rs_b200.build --target hybrid
 
-Output: vllm_rs_b200/libb200_vllm.so (git-ignored; travels to the GPU box with gpurun).
+Output: vllm_rs_b200/libb200_vllm.so (git-ignored; travels to the GPU box with gpurun).  The `hybrid` target builds
+vllm_rs_b200/libb200_hybrid.so from the sources the fp32-residual hybrid decoders need and nothing else (no tcgen05
+GEMM / attention kernels): what a fresh checkout compiles when it is first asked to serve such a model.
 """
 from __future__ import annotations
 
@@ -32,7 +35,14 @@ NVCC_FLAGS = [
 ] + os.environ.get("B200_NVCC_EXTRA", "").split()   # e.g. -DB200_DEC_TRACE (tools/dec_trace.py)
 
 
-def sources() -> list[Path]:
+HYBRID_SOURCES = ["runtime.cu", "glue.cu", "sampler.cu", "seq_norms.cu", "latent_attn.cu", "linear_recurrence.cu",
+                  "moe.cu", "gemm_lib.cu", "host/scheduler.cpp", "host/hybrid_runner.cpp"]
+HYBRID_LIB = PKG / "libb200_hybrid.so"
+
+
+def sources(target: str = "full") -> list[Path]:
+    if target == "hybrid":
+        return [CSRC / f for f in HYBRID_SOURCES]
     return sorted(list(CSRC.glob("*.cu")) + list((CSRC / "host").glob("*.cpp")))
 
 
@@ -62,10 +72,11 @@ def _compile(src: Path, force: bool) -> Path:
     return obj
 
 
-def build(force: bool = False, verbose: bool = True) -> Path:
+def build(force: bool = False, verbose: bool = True, target: str = "full") -> Path:
     BUILD.mkdir(parents=True, exist_ok=True)
+    LIB = globals()["LIB"] if target == "full" else HYBRID_LIB
     LIB.parent.mkdir(parents=True, exist_ok=True)
-    srcs = sources()
+    srcs = sources(target)
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(lambda s: _compile(s, force), srcs))
     newest = max(o.stat().st_mtime for o in objs)
@@ -83,4 +94,5 @@ def build(force: bool = False, verbose: bool = True) -> Path:
 
 
 if __name__ == "__main__":
-    build(force="--force" in sys.argv)
+    build(force="--force" in sys.argv,
+          target=sys.argv[sys.argv.index("--target") + 1] if "--target" in sys.argv else "full")

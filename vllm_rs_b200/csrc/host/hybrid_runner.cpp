@@ -1,0 +1,394 @@
+// Step runner of hybrid decoders with an fp32 residual stream: every launch of one ragged step (prompt portions and
+// decoded tokens in one batch) on one GPU.  Sibling of model_runner.cpp (the fp16 LLaMA / Qwen2 plan); like it, the
+// runner owns no device memory: weights, the paged latent cache, the state pools and one workspace come from the caller.
+//
+// Layer plan (parallel layer: mixer and feed-forward read one norm h of the stream x, both add into x):
+//   h = norm(x)                                                    resid_rmsnorm        (fp32 in, operand dtype out)
+//   latent attention:  [q | latent | k_rot] = h W_in^T             library GEMM (fp32 out)
+//                      norm + rotary + cache write + query split   latent_prep
+//                      q_abs[h] = q_plain[h] W_uk[h]               batched library GEMM into q_full
+//                      latent_attn (window, sink)                  -> attention-weighted latents
+//                      v[h] = lat[h] W_uv[h]^T ; x += v W_o^T      batched GEMM, cast, GEMM with beta = 1
+//   delta rule:        [q | k | v | b | a | gate] = h W_in^T ; short_conv_silu on q | k | v ; delta_rule ;
+//                      gated_group_norm (gate after the norm) ; x += . W_o^T
+//   SSD:               [z | x | B | C | dt] = h W_in^T ; short_conv_silu on x | B | C ; ssd_scan ;
+//                      gated_group_norm (gate before the norm) ; x += . W_o^T
+//   experts:           router GEMM (fp32 out) -> moe_route -> sort -> grouped gate|up (SiLU * mul) -> grouped down ->
+//                      combine into x ; shared expert: GEMM, silu_mul, GEMM with beta = 1 into x
+// The residual add of every branch is the beta = 1 accumulation of its last matrix product (or the combine kernel).
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "../../../include/b200_vllm.h"
+#include "../seqmix.cuh"
+
+using namespace b200;
+namespace b200 {
+long long launch_count();
+void launch_sample_topk_topp(uint32_t* out_ids, const float* logits, int B, int V, int k, float p, float t,
+                             const uint64_t* seed_dev, cudaStream_t st);
+}
+
+namespace {
+inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+}
+
+struct b200_hybrid {
+  b200_hybrid_config cfg;
+  std::vector<b200_hybrid_layer> layers;
+  const void *embed = nullptr, *final_norm = nullptr, *lm_head = nullptr;
+  uint8_t* ws = nullptr;
+  float* trace = nullptr;
+  // workspace carve-up
+  float* x = nullptr;          // [T, width] residual stream
+  void* h = nullptr;           // [T, width] normed stream, operand dtype
+  float* proj = nullptr;       // [T, max fused input projection]
+  float* aux = nullptr;        // [T, max(heads (kv_rank + rot_dim), heads vdim)] fp32: q_full / scan output / expanded values
+  void* opa = nullptr;         // [T, max(heads dim, heads vdim, 2 shared... )] operand dtype: q_plain, then the o-projection input
+  void* lat = nullptr;         // [T, heads kv_rank] operand dtype: attention-weighted latents
+  float* rlog = nullptr;       // [T, experts]
+  int32_t* top_idx = nullptr;
+  float* top_w = nullptr;
+  void* moe_ws = nullptr;
+  float* sh = nullptr;         // [T, 2 shared_ff] fp32
+  void* sha = nullptr;         // [T, shared_ff] operand dtype
+  float* xr = nullptr;         // unused rows of the stream gathered for the head: norm reads x through out_rows
+  void* hr = nullptr;          // [R, width]
+  float* logits = nullptr;     // [R, vocab]
+  // device staging of the host entry point
+  uint32_t *s_ids = nullptr, *s_cu = nullptr, *s_ctx = nullptr, *s_bt = nullptr, *s_rows = nullptr, *s_out = nullptr;
+  int64_t *s_pos = nullptr, *s_slot = nullptr;
+  int32_t* s_state = nullptr;
+  uint64_t* s_seed = nullptr;
+  int samp_k = 0;
+  bool samp_all = false;
+  float samp_p = 1.f, samp_t = 1.f;
+  int64_t launches = 0;
+};
+
+static int in_rows(const b200_hybrid_layer& l) {
+  switch (l.mixer) {
+    case B200_MIXER_LATENT_ATTN: return l.heads * (l.dim + l.rot_dim) + l.kv_rank + l.rot_dim;
+    case B200_MIXER_DELTA_RULE: return 2 * l.kv_heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads;
+    default: return 2 * l.heads * l.vdim + 2 * l.kv_heads * l.state + l.heads;
+  }
+}
+
+static int64_t carve(b200_hybrid* r, uint8_t* base) {
+  const b200_hybrid_config& c = r->cfg;
+  const size_t T = c.max_tokens, es = c.dt ? 4 : 2;
+  size_t proj_n = 1, aux_n = 1, opa_n = 1, lat_n = 1, E = 1, top = 1, sh_n = 1, moe_bytes = 256;
+  for (const b200_hybrid_layer& l : r->layers) {
+    proj_n = std::max<size_t>(proj_n, in_rows(l));
+    if (l.mixer == B200_MIXER_LATENT_ATTN) {
+      aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * std::max(l.kv_rank + l.rot_dim, l.vdim));
+      opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * std::max(l.dim, l.vdim));
+      lat_n = std::max<size_t>(lat_n, static_cast<size_t>(l.heads) * l.kv_rank);
+    } else {
+      aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * l.vdim);
+      opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * l.vdim);
+    }
+    if (l.experts > 0) {
+      E = std::max<size_t>(E, l.experts);
+      top = std::max<size_t>(top, l.top);
+      moe_bytes = std::max<size_t>(moe_bytes, b200_moe_workspace_bytes(c.max_tokens, l.experts, l.top, c.width, l.expert_ff));
+    }
+    sh_n = std::max<size_t>(sh_n, l.shared_ff);
+  }
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t* p = base ? base + off : nullptr;
+    off = up256(off + bytes);
+    return p;
+  };
+  r->x = (float*)take(T * c.width * 4);
+  r->h = take(T * c.width * es);
+  r->proj = (float*)take(T * proj_n * 4);
+  r->aux = (float*)take(T * aux_n * 4);
+  r->opa = take(T * opa_n * es);
+  r->lat = take(T * lat_n * es);
+  r->rlog = (float*)take(T * E * 4);
+  r->top_idx = (int32_t*)take(T * top * 4);
+  r->top_w = (float*)take(T * top * 4);
+  r->moe_ws = take(moe_bytes);
+  r->sh = (float*)take(T * 2 * sh_n * 4);
+  r->sha = take(T * sh_n * es);
+  r->hr = take(T * c.width * es);
+  r->logits = (float*)take(T * static_cast<size_t>(c.vocab) * 4);
+  r->s_ids = (uint32_t*)take(T * 4);
+  r->s_pos = (int64_t*)take(T * 8);
+  r->s_slot = (int64_t*)take(T * 8);
+  r->s_rows = (uint32_t*)take(T * 4);
+  r->s_out = (uint32_t*)take(T * 4);
+  r->s_cu = (uint32_t*)take((c.max_seqs + 1) * 4);
+  r->s_ctx = (uint32_t*)take(c.max_seqs * 4);
+  r->s_state = (int32_t*)take(c.max_seqs * 4);
+  r->s_bt = (uint32_t*)take(static_cast<size_t>(c.max_seqs) * c.max_blocks_per_seq * 4);
+  r->s_seed = (uint64_t*)take(8);
+  return static_cast<int64_t>(off);
+}
+
+extern "C" {
+
+b200_hybrid* b200_hybrid_new(const b200_hybrid_config* cfg) {
+  if (!cfg || cfg->width <= 0 || cfg->vocab <= 0 || cfg->num_layers <= 0 || cfg->block_size != seqmix::kPage ||
+      cfg->max_seqs <= 0 || cfg->max_tokens <= 0 || (cfg->dt != 0 && cfg->dt != 1)) {
+    set_error(1, "hybrid_new: bad config");
+    return nullptr;
+  }
+  auto* r = new b200_hybrid();
+  r->cfg = *cfg;
+  r->layers.resize(cfg->num_layers);
+  std::memset(r->layers.data(), 0, sizeof(b200_hybrid_layer) * cfg->num_layers);
+  return r;
+}
+
+void b200_hybrid_free(b200_hybrid* r) { delete r; }
+
+void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_layer* l) {
+  if (layer < 0 || layer >= r->cfg.num_layers || !l) {
+    set_error(1, "hybrid_set_layer: layer out of range");
+    return;
+  }
+  bool ok = l->heads > 0 && l->vdim > 0 && l->norm_w && l->w_in && l->w_o;
+  if (l->mixer == B200_MIXER_LATENT_ATTN)
+    ok = ok && l->kv_rank > 0 && l->w_uk && l->w_uv && l->latent_norm_w && l->kv_cache && l->rot_dims % 2 == 0 &&
+         l->rot_dims <= l->rot_dim && (l->rot_dims == 0 || l->rot_freq);
+  else if (l->mixer == B200_MIXER_DELTA_RULE)
+    ok = ok && l->kv_heads > 0 && l->heads % l->kv_heads == 0 && l->dim > 0 && l->conv_taps >= 1 && l->conv_w &&
+         l->conv_state && l->rec_state && l->a_log && l->dt_bias && l->out_norm_w;
+  else if (l->mixer == B200_MIXER_SSD)
+    ok = ok && l->kv_heads > 0 && l->heads % l->kv_heads == 0 && l->state > 0 && l->conv_taps >= 1 && l->conv_w &&
+         l->conv_state && l->rec_state && l->a_log && l->dt_bias && l->out_norm_w && l->norm_groups > 0 &&
+         (l->heads * l->vdim) % l->norm_groups == 0;
+  else
+    ok = false;
+  if (l->experts > 0) ok = ok && l->top > 0 && l->top <= l->experts && l->expert_ff > 0 && l->w_router && l->w_gate_up && l->w_down;
+  if (l->shared_ff > 0) ok = ok && l->w_shared_gate_up && l->w_shared_down;
+  if (!ok) {
+    set_error(1, "hybrid_set_layer: inconsistent layer description");
+    return;
+  }
+  r->layers[layer] = *l;
+}
+
+void b200_hybrid_set_globals(b200_hybrid* r, const void* embed, const void* final_norm, const void* lm_head) {
+  r->embed = embed;
+  r->final_norm = final_norm;
+  r->lm_head = lm_head;
+}
+
+int64_t b200_hybrid_workspace_bytes(const b200_hybrid* r) {
+  b200_hybrid tmp;
+  tmp.cfg = r->cfg;
+  tmp.layers = r->layers;
+  return carve(&tmp, nullptr) + 256;
+}
+
+void b200_hybrid_set_workspace(b200_hybrid* r, void* workspace, int64_t bytes) {
+  uint8_t* base = reinterpret_cast<uint8_t*>(up256(reinterpret_cast<size_t>(workspace)));
+  const int64_t need = carve(r, base);
+  if (need + (base - reinterpret_cast<uint8_t*>(workspace)) > bytes) {
+    set_error(1, "hybrid_set_workspace: workspace too small (set every layer before asking for its size)");
+    return;
+  }
+  r->ws = base;
+}
+
+void b200_hybrid_set_layer_trace(b200_hybrid* r, float* buf) { r->trace = buf; }
+
+int32_t b200_hybrid_set_sampling(b200_hybrid* r, int32_t strategy, int32_t k, float p, float t) {
+  if (strategy == 0) {
+    r->samp_all = false; r->samp_k = 0; r->samp_p = 1.f; r->samp_t = 1.f;
+    return 0;
+  }
+  if (strategy < 0 || strategy > 4 || !(t > 0.f) || (strategy != 1 && (k < 1 || k > 256))) {
+    set_error(1, "hybrid_set_sampling: unknown strategy or parameters out of range");
+    return -1;
+  }
+  r->samp_all = strategy == 1; r->samp_k = strategy == 1 ? 0 : k; r->samp_p = p; r->samp_t = t;
+  return 0;
+}
+
+void b200_hybrid_set_step_seed(b200_hybrid* r, uint64_t seed, int64_t stream) {
+  if (!r->ws) {
+    set_error(1, "hybrid_set_step_seed: workspace not set");
+    return;
+  }
+  cudaMemcpyAsync(r->s_seed, &seed, 8, cudaMemcpyHostToDevice, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int64_t b200_hybrid_launches_per_step(const b200_hybrid* r) { return r->launches; }
+
+static void mixer_latent(b200_hybrid* r, const b200_hybrid_layer& l, const int64_t* positions, const int64_t* slots,
+                         const uint32_t* cu, const uint32_t* ctx, const uint32_t* bt, int max_blocks, int B, int T,
+                         cudaStream_t st) {
+  const b200_hybrid_config& c = r->cfg;
+  const int H = l.heads, R = l.kv_rank + l.rot_dim, n_in = in_rows(l);
+  const size_t es = c.dt ? 4 : 2;
+  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  launch_latent_prep(r->proj, n_in, r->opa, r->aux, l.kv_cache, (const float*)l.latent_norm_w, l.rot_freq, l.rot_mag,
+                     positions, slots, T, H, l.dim, l.rot_dim, l.rot_dims, l.kv_rank, c.norm_eps, c.dt, st);
+  // q_abs[t, h, :] = q_plain[t, h, :] W_uk[h]  (W_uk[h] is [dim, kv_rank], i.e. stored [K, N])
+  if (l.dim > 0)
+    gemm_f32out(r->opa, H * l.dim, l.dim, l.w_uk, l.kv_rank, static_cast<long long>(l.dim) * l.kv_rank, r->aux, H * R, R,
+                T, l.kv_rank, l.dim, H, 0.f, 1, c.dt, st);
+  else
+    cudaMemsetAsync(r->aux, 0, static_cast<size_t>(T) * H * R * 4, st);   // (rotated parts are rewritten by prep; dim == 0 is rejected upstream)
+  launch_latent_attn(r->lat, r->aux, l.kv_cache, (const float*)l.sink, cu, ctx, bt, max_blocks, B, T, H, l.kv_rank,
+                     l.rot_dim, l.window, l.scale, c.dt, st);
+  // v[t, h, :] = lat[t, h, :] W_uv[h]^T  (W_uv[h] is [vdim, kv_rank])
+  gemm_f32out(r->lat, H * l.kv_rank, l.kv_rank, l.w_uv, l.kv_rank, static_cast<long long>(l.vdim) * l.kv_rank, r->aux,
+              H * l.vdim, l.vdim, T, l.vdim, l.kv_rank, H, 0.f, 0, c.dt, st);
+  const void* o_in = r->aux;
+  if (!c.dt) {
+    launch_cast_rows(r->opa, r->aux, H * l.vdim, T, H * l.vdim, 0, st);
+    o_in = r->opa;
+  }
+  gemm_f32out(o_in, H * l.vdim, 0, l.w_o, H * l.vdim, 0, r->x, c.width, 0, T, c.width, H * l.vdim, 1, 1.f, 0, c.dt, st);
+  (void)es;
+}
+
+static void mixer_delta(b200_hybrid* r, const b200_hybrid_layer& l, const uint32_t* cu, const uint32_t* ctx,
+                        const int32_t* state_slots, int B, int T, cudaStream_t st) {
+  const b200_hybrid_config& c = r->cfg;
+  const int H = l.heads, Hk = l.kv_heads, n_in = in_rows(l);
+  const int nq = Hk * l.dim, nv = H * l.vdim, nconv = 2 * nq + nv;
+  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  launch_short_conv_silu(r->proj, n_in, r->proj, n_in, (const float*)l.conv_w, (const float*)l.conv_b,
+                         (float*)l.conv_state, state_slots, cu, ctx, B, nconv, l.conv_taps, st);
+  const float* q = r->proj;
+  const float* k = r->proj + nq;
+  const float* v = r->proj + 2 * nq;
+  const float* b_raw = r->proj + nconv;
+  const float* a_raw = b_raw + H;
+  const float* gate = a_raw + H;
+  launch_delta_rule(r->aux, q, k, v, n_in, b_raw, a_raw, n_in, (const float*)l.a_log, (const float*)l.dt_bias,
+                    (float*)l.rec_state, state_slots, cu, ctx, B, H, Hk, l.dim, l.vdim, st);
+  launch_gated_group_norm(r->opa, r->aux, nv, gate, n_in, (const float*)l.out_norm_w, l.vdim, T, nv, l.vdim, c.norm_eps,
+                          0, c.dt, st);
+  gemm_f32out(r->opa, nv, 0, l.w_o, nv, 0, r->x, c.width, 0, T, c.width, nv, 1, 1.f, 0, c.dt, st);
+}
+
+static void mixer_ssd(b200_hybrid* r, const b200_hybrid_layer& l, const uint32_t* cu, const uint32_t* ctx,
+                      const int32_t* state_slots, int B, int T, cudaStream_t st) {
+  const b200_hybrid_config& c = r->cfg;
+  const int H = l.heads, G = l.kv_heads, N = l.state, inner = H * l.vdim, n_in = in_rows(l);
+  const int nconv = inner + 2 * G * N;
+  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  float* xbc = r->proj + inner;
+  launch_short_conv_silu(xbc, n_in, xbc, n_in, (const float*)l.conv_w, (const float*)l.conv_b, (float*)l.conv_state,
+                         state_slots, cu, ctx, B, nconv, l.conv_taps, st);
+  launch_ssd_scan(r->aux, xbc, xbc + inner, xbc + inner + G * N, n_in, xbc + nconv, n_in, (const float*)l.a_log,
+                  (const float*)l.dt_bias, (const float*)l.d_skip, (float*)l.rec_state, state_slots, cu, ctx, B, H, G, N,
+                  l.vdim, st);
+  launch_gated_group_norm(r->opa, r->aux, inner, r->proj, n_in, (const float*)l.out_norm_w, inner, T, inner,
+                          inner / l.norm_groups, c.norm_eps, 1, c.dt, st);
+  gemm_f32out(r->opa, inner, 0, l.w_o, inner, 0, r->x, c.width, 0, T, c.width, inner, 1, 1.f, 0, c.dt, st);
+}
+
+static void feed_forward(b200_hybrid* r, const b200_hybrid_layer& l, int T, cudaStream_t st) {
+  const b200_hybrid_config& c = r->cfg;
+  if (l.experts > 0) {
+    gemm_f32out(r->h, c.width, 0, l.w_router, c.width, 0, r->rlog, l.experts, 0, T, l.experts, c.width, 1, 0.f, 0, c.dt,
+                st);
+    launch_moe_route(r->rlog, T, l.experts, l.top, l.route_scale, r->top_idx, r->top_w, st);
+    b200_moe_experts(r->x, r->h, r->top_idx, r->top_w, l.w_gate_up, l.w_down, T, l.experts, l.top, c.width, l.expert_ff,
+                     c.dt, r->moe_ws, reinterpret_cast<int64_t>(st));
+  }
+  if (l.shared_ff > 0) {
+    gemm_f32out(r->h, c.width, 0, l.w_shared_gate_up, c.width, 0, r->sh, 2 * l.shared_ff, 0, T, 2 * l.shared_ff, c.width,
+                1, 0.f, 0, c.dt, st);
+    launch_silu_mul_f32(r->sha, r->sh, T, l.shared_ff, c.dt, st);
+    gemm_f32out(r->sha, l.shared_ff, 0, l.w_shared_down, l.shared_ff, 0, r->x, c.width, 0, T, c.width, l.shared_ff, 1,
+                1.f, 0, c.dt, st);
+  }
+}
+
+void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* positions, const int64_t* slot_mapping,
+                      const uint32_t* cu, const uint32_t* ctx, const uint32_t* block_tables,
+                      const int32_t* state_slots, const uint32_t* out_rows, int32_t B, int32_t T, int32_t max_blocks,
+                      int32_t num_out, float* logits, uint32_t* out_ids, int64_t stream) {
+  const b200_hybrid_config& c = r->cfg;
+  if (!r->ws || !r->embed || !r->final_norm || !r->lm_head) {
+    set_error(1, "hybrid_step: workspace or global weights not set");
+    return;
+  }
+  if (B <= 0 || B > c.max_seqs || T <= 0 || T > c.max_tokens || num_out < 0 || num_out > T) {
+    set_error(1, "hybrid_step: batch out of range");
+    return;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long launches0 = launch_count();
+  launch_embed_f32(r->x, r->embed, input_ids, T, c.width, c.vocab, c.dt, st);
+  for (int i = 0; i < c.num_layers; ++i) {
+    const b200_hybrid_layer& l = r->layers[i];
+    launch_resid_rmsnorm(r->h, r->x, (const float*)l.norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, nullptr,
+                         c.dt, st);
+    switch (l.mixer) {
+      case B200_MIXER_LATENT_ATTN:
+        mixer_latent(r, l, positions, slot_mapping, cu, ctx, block_tables, max_blocks, B, T, st);
+        break;
+      case B200_MIXER_DELTA_RULE: mixer_delta(r, l, cu, ctx, state_slots, B, T, st); break;
+      default: mixer_ssd(r, l, cu, ctx, state_slots, B, T, st); break;
+    }
+    feed_forward(r, l, T, st);
+    if (r->trace)
+      cudaMemcpyAsync(r->trace + static_cast<size_t>(i) * c.max_tokens * c.width, r->x,
+                      static_cast<size_t>(T) * c.width * 4, cudaMemcpyDeviceToDevice, st);
+  }
+  if (num_out > 0) {
+    launch_resid_rmsnorm(r->hr, r->x, (const float*)r->final_norm, num_out, c.width, c.norm_eps, c.norm_weight_offset,
+                         out_rows, c.dt, st);
+    float* lg = logits ? logits : r->logits;
+    gemm_f32out(r->hr, c.width, 0, r->lm_head, c.width, 0, lg, c.vocab, 0, num_out, c.vocab, c.width, 1, 0.f, 0, c.dt,
+                st);
+    if (out_ids) {
+      if (r->samp_k > 0 || r->samp_all)
+        launch_sample_topk_topp(out_ids, lg, num_out, c.vocab, r->samp_all ? 0 : std::min(r->samp_k, c.vocab), r->samp_p,
+                                r->samp_t, r->s_seed, st);
+      else
+        b200_argmax_f32(out_ids, lg, num_out, c.vocab, stream);
+    }
+  }
+  r->launches = launch_count() - launches0;
+}
+
+int32_t b200_hybrid_step_host(b200_hybrid* r, const uint32_t* input_ids, const int64_t* positions,
+                              const int64_t* slot_mapping, const uint32_t* cu, const uint32_t* ctx,
+                              const uint32_t* block_tables, const int32_t* state_slots, const uint32_t* out_rows,
+                              int32_t B, int32_t T, int32_t max_blocks, int32_t num_out, float* logits_host,
+                              uint32_t* out_ids_host, int64_t stream) {
+  const b200_hybrid_config& c = r->cfg;
+  if (!r->ws || B <= 0 || B > c.max_seqs || T <= 0 || T > c.max_tokens || max_blocks > c.max_blocks_per_seq ||
+      num_out < 0 || num_out > T) {
+    set_error(1, "hybrid_step_host: bad arguments");
+    return -1;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const auto H2D = cudaMemcpyHostToDevice;
+  cudaMemcpyAsync(r->s_ids, input_ids, T * 4, H2D, st);
+  cudaMemcpyAsync(r->s_pos, positions, T * 8, H2D, st);
+  cudaMemcpyAsync(r->s_slot, slot_mapping, T * 8, H2D, st);
+  cudaMemcpyAsync(r->s_cu, cu, (B + 1) * 4, H2D, st);
+  cudaMemcpyAsync(r->s_ctx, ctx, B * 4, H2D, st);
+  cudaMemcpyAsync(r->s_state, state_slots, B * 4, H2D, st);
+  cudaMemcpyAsync(r->s_bt, block_tables, static_cast<size_t>(B) * max_blocks * 4, H2D, st);
+  if (num_out > 0) cudaMemcpyAsync(r->s_rows, out_rows, num_out * 4, H2D, st);
+  b200_hybrid_step(r, r->s_ids, r->s_pos, r->s_slot, r->s_cu, r->s_ctx, r->s_bt, r->s_state, r->s_rows, B, T,
+                   max_blocks, num_out, nullptr, out_ids_host ? r->s_out : nullptr, stream);
+  if (num_out > 0 && logits_host)
+    cudaMemcpyAsync(logits_host, r->logits, static_cast<size_t>(num_out) * c.vocab * 4, cudaMemcpyDeviceToHost, st);
+  if (num_out > 0 && out_ids_host) cudaMemcpyAsync(out_ids_host, r->s_out, num_out * 4, cudaMemcpyDeviceToHost, st);
+  const cudaError_t e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) {
+    set_error(2, cudaGetErrorString(e));
+    return -1;
+  }
+  return b200_last_error() ? -1 : 0;
+}
+
+}  // extern "C"

@@ -52,6 +52,8 @@ struct Sequence {
   bool has_swapped_time = false;
   int64_t swapped_time = 0;    // ms, set by swap_out / swap-in
   std::vector<std::vector<uint32_t>> stop_token_ids;   // sampling_params.stop_token_ids
+  int32_t state_slot = -1;     // slot of the recurrent-state pools (models with state slots); kept across prefill chunks
+  bool streamed = false;       // driven by open / feed / close instead of schedule()
 
   size_t len() const { return token_ids.size(); }
   size_t num_blocks() const { return (len() + block_size - 1) / block_size; }
@@ -312,6 +314,18 @@ class BlockManager {
     }
     return true;
   }
+  // a streamed sequence received more tokens: whole blocks up to num_blocks(), no prefix lookup, all or nothing
+  bool grow(Sequence& s) {
+    const size_t need = s.num_blocks();
+    if (need > s.block_table.size() && need - s.block_table.size() > free_.size()) return false;
+    for (size_t i = s.block_table.size(); i < need; ++i) {
+      const size_t id = free_.front();
+      free_.pop_front();
+      take(id);
+      s.block_table.push_back(static_cast<uint32_t>(id));
+    }
+    return true;
+  }
   // block_manager.rs:227-231: reverse table order, freed ids go to the BACK of the list
   void deallocate(const Sequence& s) {
     for (auto it = s.block_table.rbegin(); it != s.block_table.rend(); ++it) decrement_ref(*it);
@@ -505,6 +519,13 @@ struct b200_scheduler {
   size_t block_size, max_num_seqs, max_num_batched_tokens, chunk_size;
   bool is_last_prefill = false;
   std::string err;
+  // recurrent-state slots: empty = the model has none
+  bool state_slots_on = false;
+  std::deque<int32_t> free_state_slots;
+  void release_slot(Sequence& q) {
+    if (q.state_slot >= 0) free_state_slots.push_back(q.state_slot);
+    q.state_slot = -1;
+  }
 
   b200_scheduler(size_t nb, size_t bs, size_t mns, size_t mnbt, size_t cs)
       : bm(nb, bs), block_size(bs), max_num_seqs(mns), max_num_batched_tokens(mnbt),
@@ -631,6 +652,7 @@ int32_t b200_scheduler_schedule(b200_scheduler* s, int32_t* indices, int32_t cap
     if (s->running.size() >= max_seqs_limit || scheduled.size() >= max_seqs_limit ||
         num_tokens + effective >= s->max_num_batched_tokens - 1 ||
         (seq.block_table.empty() && !s->bm.can_allocate(seq)) ||
+        (s->state_slots_on && seq.state_slot < 0 && s->free_state_slots.empty()) ||
         (s->is_last_prefill && pre_existing_running > 0)) {
       s->waiting.push_front(std::move(seq));
       break;
@@ -640,6 +662,10 @@ int32_t b200_scheduler_schedule(b200_scheduler* s, int32_t* indices, int32_t cap
         b200::set_error(1, "No free blocks available, retry later!");
         return -1;
       }
+    }
+    if (s->state_slots_on && seq.state_slot < 0) {
+      seq.state_slot = s->free_state_slots.front();
+      s->free_state_slots.pop_front();
     }
     seq.status = Status::Running;
     num_tokens += effective;
@@ -677,7 +703,7 @@ int32_t b200_scheduler_schedule(b200_scheduler* s, int32_t* indices, int32_t cap
         if (blocks < 1) blocks = 1;
         evicted = s->bm.evict_prefix_cache_blocks(blocks);
       }
-      if (evicted == 0 && !preempt.empty() && s->running.size() > 1) {
+      if (evicted == 0 && !preempt.empty() && s->running.size() > 1 && !s->state_slots_on) {
         size_t best = preempt[0];
         for (size_t i : preempt)
           if (s->running[i].id < s->running[best].id) best = i;
@@ -689,6 +715,7 @@ int32_t b200_scheduler_schedule(b200_scheduler* s, int32_t* indices, int32_t cap
   for (size_t idx = 0; idx < s->running.size(); ++idx) {
     if (decode.size() >= max_seqs_limit) break;
     Sequence& seq = s->running[idx];
+    if (seq.streamed) continue;
     if (!s->bm.can_append(seq)) continue;
     if (!s->bm.may_append(seq)) {
       b200::set_error(1, "No free blocks available, retry later!");
@@ -756,6 +783,7 @@ void b200_scheduler_postprocess(b200_scheduler* s, const int32_t* indices, int32
       seq.status = Status::Finished;
       s->bm.cache_sequence(seq);     // scheduler.rs:617-620: the cache takes its references first
       s->bm.deallocate(seq);
+      s->release_slot(seq);
     } else {
       seq.append_token(tok);
     }
@@ -1147,6 +1175,102 @@ int32_t b200_scheduler_load_sequence(b200_scheduler* s, const uint8_t* frame, in
 // KVCacheAllocator::plan_allocation for dense models
 //   /root/reference/src/utils/kvcache_allocator.rs:126-141 (kv heads per shard), 447-468
 //   (per_block_bytes), 553-612 (auto_decide_params), 616-707 (plan_allocation)
+// ---- recurrent-state slots and host-driven (streamed) sequences
+int32_t b200_scheduler_enable_state_slots(b200_scheduler* s, int32_t n) {
+  if (n <= 0 || !s->running.empty() || !s->waiting.empty()) return -1;
+  s->state_slots_on = true;
+  s->free_state_slots.clear();
+  for (int32_t i = 0; i < n; ++i) s->free_state_slots.push_back(i);
+  return n;
+}
+int32_t b200_scheduler_num_free_state_slots(const b200_scheduler* s) {
+  return static_cast<int32_t>(s->free_state_slots.size());
+}
+int32_t b200_scheduler_seq_state_slot(const b200_scheduler* s, int32_t i) {
+  if (i < 0 || static_cast<size_t>(i) >= s->running.size()) return -1;
+  return s->running[i].state_slot;
+}
+int32_t b200_scheduler_running_index(const b200_scheduler* s, int64_t seq_id) {
+  for (size_t i = 0; i < s->running.size(); ++i)
+    if (s->running[i].id == seq_id) return static_cast<int32_t>(i);
+  return -1;
+}
+int64_t b200_scheduler_open(b200_scheduler* s) {
+  if (s->state_slots_on && s->free_state_slots.empty()) return -1;
+  Sequence seq;
+  seq.block_size = s->block_size;
+  seq.streamed = true;
+  seq.status = Status::Running;
+  seq.id = s->next_seq_id++;
+  if (s->state_slots_on) {
+    seq.state_slot = s->free_state_slots.front();
+    s->free_state_slots.pop_front();
+  }
+  const int64_t id = seq.id;
+  s->running.push_back(std::move(seq));
+  return id;
+}
+int32_t b200_scheduler_feed(b200_scheduler* s, int64_t seq_id, const uint32_t* tokens, int32_t n) {
+  const int32_t i = b200_scheduler_running_index(s, seq_id);
+  if (i < 0 || n <= 0 || !s->running[i].streamed) return -2;
+  Sequence& q = s->running[i];
+  const size_t need = (q.len() + n + s->block_size - 1) / s->block_size;
+  if (need > q.block_table.size() && need - q.block_table.size() > s->bm.num_free()) return -1;   // nothing is taken
+  q.token_ids.insert(q.token_ids.end(), tokens, tokens + n);
+  q.last_token = q.token_ids.back();
+  return s->bm.grow(q) ? 0 : -1;
+}
+int32_t b200_scheduler_close(b200_scheduler* s, int64_t seq_id) {
+  const int32_t i = b200_scheduler_running_index(s, seq_id);
+  if (i < 0) return -1;
+  Sequence& q = s->running[i];
+  s->bm.deallocate(q);
+  s->release_slot(q);
+  s->running.erase(s->running.begin() + i);
+  return 0;
+}
+
+int32_t b200_prepare_ragged(b200_scheduler* s, const int32_t* indices, const int32_t* counts, int32_t n, int32_t mode,
+                            int32_t token_cap, int32_t max_blocks_cap, uint32_t* input_ids, int64_t* positions,
+                            int64_t* slot_mapping, uint32_t* cu_seqlens_q, uint32_t* context_lens,
+                            uint32_t* block_tables, int32_t* state_slots) {
+  const int64_t bs = static_cast<int64_t>(s->block_size);
+  int32_t T = 0;
+  cu_seqlens_q[0] = 0;
+  std::memset(block_tables, 0, sizeof(uint32_t) * static_cast<size_t>(n) * max_blocks_cap);
+  for (int32_t i = 0; i < n; ++i) {
+    if (indices[i] < 0 || static_cast<size_t>(indices[i]) >= s->running.size()) return -2;
+    Sequence& q = s->running[indices[i]];
+    size_t lo, hi;
+    if (mode == 1) {                       // decode: the last `count` tokens
+      const size_t c = counts ? counts[i] : 1;
+      if (c == 0 || c > q.len()) return -2;
+      lo = q.len() - c;
+      hi = q.len();
+    } else {
+      lo = q.num_cached_tokens;
+      const size_t rest = q.len() - lo;
+      const size_t c = counts ? counts[i] : (mode == 0 ? std::min(s->chunk_size, rest) : rest);
+      if (c == 0 || c > rest) return -2;
+      hi = lo + c;
+    }
+    const size_t nb = (hi + s->block_size - 1) / s->block_size;
+    if (nb > q.block_table.size()) return -2;
+    if (T + static_cast<int32_t>(hi - lo) > token_cap || static_cast<int32_t>(nb) > max_blocks_cap) return -1;
+    for (size_t p = lo; p < hi; ++p, ++T) {
+      input_ids[T] = q.token_ids[p];
+      positions[T] = static_cast<int64_t>(p);
+      slot_mapping[T] = static_cast<int64_t>(q.block_table[p / s->block_size]) * bs + static_cast<int64_t>(p % s->block_size);
+    }
+    cu_seqlens_q[i + 1] = static_cast<uint32_t>(T);
+    context_lens[i] = static_cast<uint32_t>(hi);
+    for (size_t b = 0; b < nb; ++b) block_tables[static_cast<size_t>(i) * max_blocks_cap + b] = q.block_table[b];
+    state_slots[i] = q.state_slot < 0 ? 0 : q.state_slot;
+    if (mode == 2) q.num_cached_tokens = hi;
+  }
+  return T;
+}
+
 int32_t b200_kvcache_plan_allocation(int64_t available, int32_t num_layers, int32_t num_kv_heads,
                                      int32_t head_dim, int32_t num_shards, int32_t block_size,
                                      int32_t dtype_size, int64_t config_model_len,

@@ -1,0 +1,237 @@
+// Latent (compressed-KV) attention over the paged cache, for ragged steps (prompt portions and decoded tokens alike).
+//
+// The cache holds ONE row per token and layer: [c (kv_rank) | k_rot (rot_dim)], c = the RMS-normed latent, k_rot the
+// rotated key part shared by all heads.  Pages are the block manager's 64-token blocks:
+//   cache [num_blocks, 64, kv_rank + rot_dim]   (bf16 or fp32).
+// Queries come in "absorbed" form: q_full [T, H, kv_rank + rot_dim] fp32 where the first kv_rank entries are
+// W_uk[h]^T q_plain[h] (a batched matrix product made by the runner) and the rest the rotated query part, so that
+//   score(i, j, h) = (q_full[i, h] . cache[j]) * scale
+// and the kernel returns the attention-weighted LATENT sum_j p_j c_j [T, H, kv_rank]; the runner expands it with
+// W_uv[h].  All heads of a token read the same cache rows (multi-query form), which is what makes the latent cache
+// cheap to stream.  Options: sliding window (position i sees j with 0 <= i - j < window; window <= 0 = all), and a
+// learned per-head sink logit that joins the softmax denominator without a key or value.
+// Beside paged_attn_decode.cu / attn_prefill*.cu (per-head K / V caches, fp16 / bf16, no window over prompts).
+//
+// latent_prep_kernel: from the fused projection row [q (H x (dim + rot_dim)) | c_raw (kv_rank) | k_rot_raw (rot_dim)]
+// (fp32) it RMS-norms the latent (plain weight), rotates the first rot_dims entries of every head's rotated query
+// part and of the shared key part as interleaved pairs (2i, 2i+1) by the angle position * freq[i] (angles in double,
+// cos / sin scaled by rot_mag), writes the cache row at the token's slot, and splits the queries.
+#include "../../include/b200_vllm.h"
+#include "seqmix.cuh"
+
+namespace b200 {
+using namespace seqmix;
+
+template <typename T>
+__global__ void latent_prep_kernel(const float* __restrict__ qc, int ldq, T* __restrict__ q_plain,
+                                   float* __restrict__ q_full, T* __restrict__ cache,
+                                   const float* __restrict__ latent_norm_w, const double* __restrict__ rot_freq,
+                                   float rot_mag, const int64_t* __restrict__ positions,
+                                   const int64_t* __restrict__ slots, int heads, int dim, int rot_dim, int rot_dims,
+                                   int kv_rank, float eps) {
+  extern __shared__ float sm[];          // cos[rot_dims/2] | sin[rot_dims/2] | red[33]
+  const int half = rot_dims / 2;
+  float* cs = sm;
+  float* sn = sm + half;
+  float* red = sm + 2 * half;
+  const int t = blockIdx.x;
+  const float* row = qc + static_cast<size_t>(t) * ldq;
+  const float* craw = row + static_cast<size_t>(heads) * (dim + rot_dim);
+  const float* kraw = craw + kv_rank;
+  const double pos = static_cast<double>(positions[t]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double s, c;
+    sincos(pos * rot_freq[i], &s, &c);
+    cs[i] = static_cast<float>(c) * rot_mag;
+    sn[i] = static_cast<float>(s) * rot_mag;
+  }
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) ss += craw[d] * craw[d];
+  ss = block_sum(ss, red);           // also orders the cos / sin writes before their use
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(kv_rank) + eps);
+  const int64_t slot = slots[t];
+  const int R = kv_rank + rot_dim;
+  if (slot >= 0) {
+    T* crow = cache + static_cast<size_t>(slot) * R;
+    for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) st(crow + d, craw[d] * inv * latent_norm_w[d]);
+    for (int d = threadIdx.x; d < rot_dim; d += blockDim.x) {
+      float v = kraw[d];
+      if (d < rot_dims) {
+        const int i = d >> 1;
+        const float a = kraw[2 * i], b = kraw[2 * i + 1];
+        v = (d & 1) ? b * cs[i] + a * sn[i] : a * cs[i] - b * sn[i];
+      }
+      st(crow + kv_rank + d, v);
+    }
+  }
+  const int hd = dim + rot_dim;
+  for (int e = threadIdx.x; e < heads * hd; e += blockDim.x) {
+    const int h = e / hd, d = e % hd;
+    const float* qh = row + static_cast<size_t>(h) * hd;
+    if (d < dim) {
+      st(q_plain + (static_cast<size_t>(t) * heads + h) * dim + d, qh[d]);
+    } else {
+      const int r = d - dim;
+      float v = qh[d];
+      if (r < rot_dims) {
+        const int i = r >> 1;
+        const float a = qh[dim + 2 * i], b = qh[dim + 2 * i + 1];
+        v = (r & 1) ? b * cs[i] + a * sn[i] : a * cs[i] - b * sn[i];
+      }
+      q_full[(static_cast<size_t>(t) * heads + h) * R + kv_rank + r] = v;
+    }
+  }
+}
+
+// grid = (token rows, head groups); a block's warps each own one head at a time.  Key rows of a tile are staged once
+// in shared memory (fp32) and used by every head of the group.
+template <typename T>
+__global__ void latent_attn_kernel(T* __restrict__ out, const float* __restrict__ q_full, const T* __restrict__ cache,
+                                   const float* __restrict__ sink, const uint32_t* __restrict__ cu,
+                                   const uint32_t* __restrict__ ctx, const uint32_t* __restrict__ block_tables,
+                                   int max_blocks, int num_seqs, int heads, int kv_rank, int rot_dim, int window,
+                                   float scale, int key_tile) {
+  extern __shared__ float sm[];
+  const int R = kv_rank + rot_dim, Rp = R | 1;        // odd row pitch: a lane per key reads conflict-free
+  const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* ks = sm;                                      // [key_tile][Rp]
+  float* qs = ks + static_cast<size_t>(key_tile) * Rp;  // [nw][R]
+  float* os = qs + static_cast<size_t>(nw) * R;        // [nw][kv_rank]
+  const int t = blockIdx.x;
+  const int b = seq_of_row(cu, num_seqs, t);
+  const int qlen = static_cast<int>(cu[b + 1] - cu[b]);
+  const int pos = static_cast<int>(ctx[b]) - qlen + (t - static_cast<int>(cu[b]));
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int h = blockIdx.y * nw + warp;
+  const bool live = h < heads;
+  if (live) {
+    const float* q = q_full + (static_cast<size_t>(t) * heads + h) * R;
+    for (int d = lane; d < R; d += 32) qs[warp * R + d] = q[d];
+    for (int d = lane; d < kv_rank; d += 32) os[warp * kv_rank + d] = 0.f;
+  }
+  float m = -1e30f, l = 0.f;
+  if (live && sink) {
+    m = sink[h];
+    l = 1.f;
+  }
+  const uint32_t* bt = block_tables + static_cast<size_t>(b) * max_blocks;
+  for (int j0 = lo; j0 <= pos; j0 += key_tile) {
+    const int nk = min(key_tile, pos - j0 + 1);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nk * R; e += blockDim.x) {
+      const int k = e / R, d = e % R, j = j0 + k;
+      const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
+      ks[k * Rp + d] = ld(cache + slot * R + d);
+    }
+    __syncthreads();
+    if (!live) continue;
+    for (int k0 = 0; k0 < nk; k0 += 32) {
+      const int k = k0 + lane;
+      float s = -1e30f;
+      if (k < nk) {
+        float acc = 0.f;
+        const float* kr = ks + k * Rp;
+        const float* qw = qs + warp * R;
+        for (int d = 0; d < R; ++d) acc += qw[d] * kr[d];
+        s = acc * scale;
+      }
+      const float mt = lanes_max(s);
+      const float mn = fmaxf(m, mt);
+      const float alpha = expf(m - mn);
+      const float p = k < nk ? expf(s - mn) : 0.f;
+      l = l * alpha + lanes_sum(p);
+      m = mn;
+      const int cnt = min(32, nk - k0);
+      for (int d0 = 0; d0 < kv_rank; d0 += 32) {       // every lane takes part in the shuffles
+        const int d = d0 + lane;
+        const bool ok = d < kv_rank;
+        float acc = ok ? os[warp * kv_rank + d] * alpha : 0.f;
+        for (int kk = 0; kk < cnt; ++kk) {
+          const float pk = __shfl_sync(0xffffffffu, p, kk);
+          if (ok) acc += pk * ks[(k0 + kk) * Rp + d];
+        }
+        if (ok) os[warp * kv_rank + d] = acc;
+      }
+    }
+  }
+  if (live) {
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    T* o = out + (static_cast<size_t>(t) * heads + h) * kv_rank;
+    for (int d = lane; d < kv_rank; d += 32) st(o + d, os[warp * kv_rank + d] * inv);
+  }
+}
+
+void launch_latent_prep(const float* qc, int ldq, void* q_plain, float* q_full, void* cache, const float* latent_norm_w,
+                        const double* rot_freq, float rot_mag, const int64_t* positions, const int64_t* slots, int T,
+                        int heads, int dim, int rot_dim, int rot_dims, int kv_rank, float eps, int dt, cudaStream_t st_) {
+  if (T <= 0) return;
+  const size_t smem = (static_cast<size_t>(rot_dims) + 40) * 4;
+  if (dt)
+    latent_prep_kernel<float><<<T, 256, smem, st_>>>(qc, ldq, (float*)q_plain, q_full, (float*)cache, latent_norm_w,
+                                                     rot_freq, rot_mag, positions, slots, heads, dim, rot_dim,
+                                                     rot_dims, kv_rank, eps);
+  else
+    latent_prep_kernel<__nv_bfloat16><<<T, 256, smem, st_>>>(qc, ldq, (__nv_bfloat16*)q_plain, q_full,
+                                                             (__nv_bfloat16*)cache, latent_norm_w, rot_freq, rot_mag,
+                                                             positions, slots, heads, dim, rot_dim, rot_dims, kv_rank,
+                                                             eps);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_latent_attn(void* out, const float* q_full, const void* cache, const float* sink, const uint32_t* cu,
+                        const uint32_t* ctx, const uint32_t* block_tables, int max_blocks, int num_seqs, int T,
+                        int heads, int kv_rank, int rot_dim, int window, float scale, int dt, cudaStream_t st_) {
+  if (T <= 0) return;
+  const int R = kv_rank + rot_dim, Rp = R | 1;
+  const int nw = heads >= 8 ? 8 : (heads >= 4 ? 4 : (heads >= 2 ? 2 : 1));
+  int key_tile = 32;
+  auto bytes = [&](int kt) { return (static_cast<size_t>(kt) * Rp + static_cast<size_t>(nw) * (R + kv_rank)) * 4; };
+  while (key_tile > 1 && bytes(key_tile) > 200 * 1024) key_tile >>= 1;
+  const size_t smem = bytes(key_tile);
+  if (smem > 220 * 1024) {
+    set_error(1, "latent_attn: kv_rank + rot_dim too large for the shared-memory tile");
+    return;
+  }
+  const dim3 grid(T, (heads + nw - 1) / nw);
+  if (dt) {
+    auto kern = latent_attn_kernel<float>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, nw * 32, smem, st_>>>((float*)out, q_full, (const float*)cache, sink, cu, ctx, block_tables,
+                                       max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale, key_tile);
+  } else {
+    auto kern = latent_attn_kernel<__nv_bfloat16>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, nw * 32, smem, st_>>>((__nv_bfloat16*)out, q_full, (const __nv_bfloat16*)cache, sink, cu, ctx,
+                                       block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale,
+                                       key_tile);
+  }
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+}  // namespace b200
+
+extern "C" {
+void b200_latent_prep(const float* qc, int32_t ldq, void* q_plain, float* q_full, void* cache,
+                      const float* latent_norm_w, const double* rot_freq, float rot_mag, const int64_t* positions,
+                      const int64_t* slot_mapping, int32_t num_tokens, int32_t heads, int32_t dim, int32_t rot_dim,
+                      int32_t rot_dims, int32_t kv_rank, float eps, int32_t dt, int64_t stream) {
+  B200_CHECK_ARG(qc && q_plain && q_full && cache && latent_norm_w && rot_freq && positions && slot_mapping &&
+                     heads > 0 && dim >= 0 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim &&
+                     rot_dims % 2 == 0 && kv_rank > 0 && (dt == 0 || dt == 1),
+                 "latent_prep: bad arguments");
+  b200::launch_latent_prep(qc, ldq, q_plain, q_full, cache, latent_norm_w, rot_freq, rot_mag, positions, slot_mapping,
+                           num_tokens, heads, dim, rot_dim, rot_dims, kv_rank, eps, dt,
+                           reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_latent_attn(void* out, const float* q_full, const void* cache, const float* sink,
+                      const uint32_t* cu_seqlens_q, const uint32_t* context_lens, const uint32_t* block_tables,
+                      int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens, int32_t heads, int32_t kv_rank,
+                      int32_t rot_dim, int32_t window, float scale, int32_t dt, int64_t stream) {
+  B200_CHECK_ARG(out && q_full && cache && cu_seqlens_q && context_lens && block_tables && num_seqs > 0 && heads > 0 &&
+                     kv_rank > 0 && rot_dim >= 0 && (dt == 0 || dt == 1),
+                 "latent_attn: bad arguments");
+  b200::launch_latent_attn(out, q_full, cache, sink, cu_seqlens_q, context_lens, block_tables, max_blocks_per_seq,
+                           num_seqs, num_tokens, heads, kv_rank, rot_dim, window, scale, dt,
+                           reinterpret_cast<cudaStream_t>(stream));
+}
+}

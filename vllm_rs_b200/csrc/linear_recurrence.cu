@@ -1,0 +1,286 @@
+// Recurrent sequence mixers with a per-sequence state slot, for ragged steps (a prompt portion of any length or one
+// decoded token per sequence): the short causal convolution in front of them, the gated delta rule, and the
+// scalar-decay state-space scan (SSD form of Mamba-2).  State lives in fp32 in slot-indexed pools owned by the caller;
+// a sequence that starts at position 0 in this step (context == rows of the step) starts from zeros whatever its
+// slot held before, so slots can be handed on without clearing.  Everything here is fp32.
+//
+//   short_conv_silu : y[t, c] = silu(bias[c] + sum_j w[c, j] * x[t - (taps-1) + j, c]); the last taps-1 inputs of a
+//                     sequence are its conv state  [slots, taps-1, C].
+//   delta_rule      : per head, S [dim, vdim]:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//                     with q, k unit-normalised per head (q also times dim^-1/2), beta = sigmoid(b),
+//                     g = exp(-exp(a_log) * softplus(a + dt_bias)).  state [slots, heads, dim, vdim].
+//   ssd_scan        : per head, S [nstate, vdim]:  dt = softplus(dt_raw + dt_bias);  S <- exp(-exp(a_log) dt) S + dt B x^T;
+//                     y = S^T C + D x.  state [slots, heads, nstate, vdim].
+// In both scans a thread owns one column of S (one value channel) in registers and walks the sequence's tokens in
+// order: the exact recurrence, no chunked reformulation, so a portion boundary cannot change the arithmetic.
+#include "../../include/b200_vllm.h"
+#include "seqmix.cuh"
+
+namespace b200 {
+using namespace seqmix;
+
+constexpr int kMaxTaps = 8;
+
+template <int TAPS>
+__global__ void short_conv_silu_kernel(float* __restrict__ out, int ldo, const float* __restrict__ x, int ldx,
+                                       const float* __restrict__ taps_w, const float* __restrict__ bias,
+                                       float* __restrict__ state, const int32_t* __restrict__ slots,
+                                       const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx, int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (c >= C) return;
+  const int t0 = cu[b], t1 = cu[b + 1];
+  if (t1 <= t0) return;
+  const bool fresh = static_cast<int>(ctx[b]) == t1 - t0;
+  constexpr int P = TAPS - 1;                  // inputs remembered between tokens
+  float w[TAPS], win[P > 0 ? P : 1];
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) w[j] = taps_w[static_cast<size_t>(c) * TAPS + j];
+  float* sp = state + static_cast<size_t>(slots[b]) * P * C + c;
+#pragma unroll
+  for (int j = 0; j < P; ++j) win[j] = fresh ? 0.f : sp[static_cast<size_t>(j) * C];     // oldest first
+  const float bv = bias ? bias[c] : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const float xv = x[static_cast<size_t>(t) * ldx + c];
+    float acc = bv;
+#pragma unroll
+    for (int j = 0; j < P; ++j) acc += w[j] * win[j];
+    acc += w[P] * xv;
+    out[static_cast<size_t>(t) * ldo + c] = silu_exact(acc);
+#pragma unroll
+    for (int j = 0; j + 1 < P; ++j) win[j] = win[j + 1];
+    if (P > 0) win[P > 0 ? P - 1 : 0] = xv;
+  }
+#pragma unroll
+  for (int j = 0; j < P; ++j) sp[static_cast<size_t>(j) * C] = win[j];
+}
+
+constexpr int kChunk = 8;          // tokens staged in shared memory per pass
+
+// grid = (column blocks, heads, sequences); DK = compile-time bound of `dim` (rows of S held per thread)
+template <int DK>
+__global__ void __launch_bounds__(128)
+delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k,
+                  const float* __restrict__ v, int ld, const float* __restrict__ b_raw,
+                  const float* __restrict__ a_raw, int ld_ba, const float* __restrict__ a_log,
+                  const float* __restrict__ dt_bias, float* __restrict__ state, const int32_t* __restrict__ slots,
+                  const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx, int heads, int kv_heads, int dim,
+                  int vdim) {
+  __shared__ float ks[kChunk][DK], qs[kChunk][DK], gs[kChunk], bs[kChunk];
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = col < vdim;
+  const int t0 = cu[b], t1 = cu[b + 1];
+  if (t1 <= t0) return;
+  const bool fresh = static_cast<int>(ctx[b]) == t1 - t0;
+  const int hk = h / (heads / kv_heads);
+  float* sp = state + ((static_cast<size_t>(slots[b]) * heads + h) * dim) * vdim + col;
+  float s[DK];
+#pragma unroll
+  for (int i = 0; i < DK; ++i) s[i] = (!fresh && live && i < dim) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
+  const float neg_a = -expf(a_log[h]), dtb = dt_bias[h], qscale = rsqrtf(static_cast<float>(dim));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int c0 = t0; c0 < t1; c0 += kChunk) {
+    const int n = min(kChunk, t1 - c0);
+    __syncthreads();
+    // stage and unit-normalise q, k of the chunk: one warp per token row
+    for (int r = warp; r < n; r += nw) {
+      const float* kr = k + static_cast<size_t>(c0 + r) * ld + hk * dim;
+      const float* qr = q + static_cast<size_t>(c0 + r) * ld + hk * dim;
+      float sk = 0.f, sq = 0.f;
+      for (int i = lane; i < dim; i += 32) {
+        sk += kr[i] * kr[i];
+        sq += qr[i] * qr[i];
+      }
+      sk = lanes_sum(sk);
+      sq = lanes_sum(sq);
+      const float ik = 1.f / sqrtf(sk + 1e-6f), iq = qscale / sqrtf(sq + 1e-6f);
+      for (int i = lane; i < DK; i += 32) {
+        ks[r][i] = i < dim ? kr[i] * ik : 0.f;
+        qs[r][i] = i < dim ? qr[i] * iq : 0.f;
+      }
+      if (lane == 0) {
+        bs[r] = sigmoid_f(b_raw[static_cast<size_t>(c0 + r) * ld_ba + h]);
+        gs[r] = expf(neg_a * softplus_f(a_raw[static_cast<size_t>(c0 + r) * ld_ba + h] + dtb));
+      }
+    }
+    __syncthreads();
+    if (!live) continue;
+    for (int r = 0; r < n; ++r) {
+      const float g = gs[r];
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < DK; ++i) {
+        s[i] *= g;
+        dot += ks[r][i] * s[i];
+      }
+      const float u = bs[r] * (v[static_cast<size_t>(c0 + r) * ld + h * vdim + col] - dot);
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < DK; ++i) {
+        s[i] += ks[r][i] * u;
+        o += qs[r][i] * s[i];
+      }
+      out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = o;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < DK; ++i)
+      if (i < dim) sp[static_cast<size_t>(i) * vdim] = s[i];
+  }
+}
+
+template <int NS>
+__global__ void __launch_bounds__(128)
+ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ Bm,
+                const float* __restrict__ Cm, int ld, const float* __restrict__ dt_raw, int ld_dt,
+                const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ d_skip,
+                float* __restrict__ state, const int32_t* __restrict__ slots, const uint32_t* __restrict__ cu,
+                const uint32_t* __restrict__ ctx, int heads, int groups, int nstate, int vdim) {
+  __shared__ float Bs[kChunk][NS], Cs[kChunk][NS], dts[kChunk], das[kChunk];
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = col < vdim;
+  const int t0 = cu[b], t1 = cu[b + 1];
+  if (t1 <= t0) return;
+  const bool fresh = static_cast<int>(ctx[b]) == t1 - t0;
+  const int g = h / (heads / groups);
+  float* sp = state + ((static_cast<size_t>(slots[b]) * heads + h) * nstate) * vdim + col;
+  float s[NS];
+#pragma unroll
+  for (int i = 0; i < NS; ++i) s[i] = (!fresh && live && i < nstate) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
+  const float neg_a = -expf(a_log[h]), dtb = dt_bias[h], dsk = d_skip ? d_skip[h] : 0.f;
+  for (int c0 = t0; c0 < t1; c0 += kChunk) {
+    const int n = min(kChunk, t1 - c0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < n * NS; e += blockDim.x) {
+      const int r = e / NS, i = e % NS;
+      Bs[r][i] = i < nstate ? Bm[static_cast<size_t>(c0 + r) * ld + g * nstate + i] : 0.f;
+      Cs[r][i] = i < nstate ? Cm[static_cast<size_t>(c0 + r) * ld + g * nstate + i] : 0.f;
+    }
+    if (threadIdx.x < n) {
+      const float dt = softplus_f(dt_raw[static_cast<size_t>(c0 + threadIdx.x) * ld_dt + h] + dtb);
+      dts[threadIdx.x] = dt;
+      das[threadIdx.x] = expf(neg_a * dt);
+    }
+    __syncthreads();
+    if (!live) continue;
+    for (int r = 0; r < n; ++r) {
+      const float xv = x[static_cast<size_t>(c0 + r) * ld + h * vdim + col];
+      const float a = das[r], dx = dts[r] * xv;
+      float y = 0.f;
+#pragma unroll
+      for (int i = 0; i < NS; ++i) {
+        s[i] = a * s[i] + dx * Bs[r][i];
+        y += Cs[r][i] * s[i];
+      }
+      out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = y + dsk * xv;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NS; ++i)
+      if (i < nstate) sp[static_cast<size_t>(i) * vdim] = s[i];
+  }
+}
+
+void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const float* taps_w, const float* bias,
+                            float* state, const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs,
+                            int C, int taps, cudaStream_t st_) {
+  if (num_seqs <= 0 || C <= 0) return;
+  if (taps < 1 || taps > kMaxTaps) {
+    set_error(1, "short_conv: between 1 and 8 taps are supported");
+    return;
+  }
+  const dim3 grid((C + 127) / 128, num_seqs);
+#define B200_CONV(K)                                                                                              \
+  case K:                                                                                                         \
+    short_conv_silu_kernel<K><<<grid, 128, 0, st_>>>(out, ldo, x, ldx, taps_w, bias, state, slots, cu, ctx, C); \
+    break
+  switch (taps) {
+    B200_CONV(1); B200_CONV(2); B200_CONV(3); B200_CONV(4); B200_CONV(5); B200_CONV(6); B200_CONV(7); B200_CONV(8);
+  }
+#undef B200_CONV
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+static int col_threads(int vdim) { return vdim >= 128 ? 128 : (vdim > 32 ? 64 : 32); }
+
+void launch_delta_rule(float* out, const float* q, const float* k, const float* v, int ld, const float* b_raw,
+                       const float* a_raw, int ld_ba, const float* a_log, const float* dt_bias, float* state,
+                       const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads,
+                       int kv_heads, int dim, int vdim, cudaStream_t st_) {
+  if (num_seqs <= 0) return;
+  const int th = col_threads(vdim);
+  const dim3 grid((vdim + th - 1) / th, heads, num_seqs);
+#define B200_DELTA(DK)                                                                                              \
+  delta_rule_kernel<DK><<<grid, th, 0, st_>>>(out, q, k, v, ld, b_raw, a_raw, ld_ba, a_log, dt_bias, state, slots, \
+                                              cu, ctx, heads, kv_heads, dim, vdim)
+  if (dim <= 16) B200_DELTA(16);
+  else if (dim <= 32) B200_DELTA(32);
+  else if (dim <= 64) B200_DELTA(64);
+  else if (dim <= 128) B200_DELTA(128);
+  else if (dim <= 256) B200_DELTA(256);
+  else {
+    set_error(1, "delta_rule: key dimension above 256 is not supported");
+    return;
+  }
+#undef B200_DELTA
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_ssd_scan(float* out, const float* x, const float* Bm, const float* Cm, int ld, const float* dt_raw,
+                     int ld_dt, const float* a_log, const float* dt_bias, const float* d_skip, float* state,
+                     const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads, int groups,
+                     int nstate, int vdim, cudaStream_t st_) {
+  if (num_seqs <= 0) return;
+  const int th = col_threads(vdim);
+  const dim3 grid((vdim + th - 1) / th, heads, num_seqs);
+#define B200_SSD(NS)                                                                                               \
+  ssd_scan_kernel<NS><<<grid, th, 0, st_>>>(out, x, Bm, Cm, ld, dt_raw, ld_dt, a_log, dt_bias, d_skip, state, slots, \
+                                            cu, ctx, heads, groups, nstate, vdim)
+  if (nstate <= 16) B200_SSD(16);
+  else if (nstate <= 32) B200_SSD(32);
+  else if (nstate <= 64) B200_SSD(64);
+  else if (nstate <= 128) B200_SSD(128);
+  else if (nstate <= 256) B200_SSD(256);
+  else {
+    set_error(1, "ssd_scan: state size above 256 is not supported");
+    return;
+  }
+#undef B200_SSD
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+}  // namespace b200
+
+extern "C" {
+void b200_short_conv_silu(float* out, int32_t ldo, const float* x, int32_t ldx, const float* taps_w, const float* bias,
+                          float* state, const int32_t* state_slots, const uint32_t* cu_seqlens_q,
+                          const uint32_t* context_lens, int32_t num_seqs, int32_t channels, int32_t taps,
+                          int64_t stream) {
+  B200_CHECK_ARG(out && x && taps_w && state && state_slots && cu_seqlens_q && context_lens, "short_conv: bad arguments");
+  b200::launch_short_conv_silu(out, ldo, x, ldx, taps_w, bias, state, state_slots, cu_seqlens_q, context_lens, num_seqs,
+                               channels, taps, reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_delta_rule(float* out, const float* q, const float* k, const float* v, int32_t ld, const float* b_raw,
+                     const float* a_raw, int32_t ld_ba, const float* a_log, const float* dt_bias, float* state,
+                     const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                     int32_t num_seqs, int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int64_t stream) {
+  B200_CHECK_ARG(out && q && k && v && b_raw && a_raw && a_log && dt_bias && state && state_slots && cu_seqlens_q &&
+                     context_lens && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0,
+                 "delta_rule: bad arguments");
+  b200::launch_delta_rule(out, q, k, v, ld, b_raw, a_raw, ld_ba, a_log, dt_bias, state, state_slots, cu_seqlens_q,
+                          context_lens, num_seqs, heads, kv_heads, dim, vdim, reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_ssd_scan(float* out, const float* x, const float* Bm, const float* Cm, int32_t ld, const float* dt_raw,
+                   int32_t ld_dt, const float* a_log, const float* dt_bias, const float* d_skip, float* state,
+                   const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                   int32_t num_seqs, int32_t heads, int32_t groups, int32_t nstate, int32_t vdim, int64_t stream) {
+  B200_CHECK_ARG(out && x && Bm && Cm && dt_raw && a_log && dt_bias && state && state_slots && cu_seqlens_q &&
+                     context_lens && heads > 0 && groups > 0 && heads % groups == 0 && nstate > 0 && vdim > 0,
+                 "ssd_scan: bad arguments");
+  b200::launch_ssd_scan(out, x, Bm, Cm, ld, dt_raw, ld_dt, a_log, dt_bias, d_skip, state, state_slots, cu_seqlens_q,
+                        context_lens, num_seqs, heads, groups, nstate, vdim, reinterpret_cast<cudaStream_t>(stream));
+}
+}

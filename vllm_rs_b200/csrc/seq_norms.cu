@@ -1,0 +1,163 @@
+// Row kernels of decoders that keep the residual stream in fp32: embedding lookup into the stream, RMS norm of the
+// stream (weight stored either plainly or as an offset from one), the grouped RMS norm with a SiLU gate that follows
+// a recurrent mixer (gate applied before or after the normalisation), SiLU * mul over an fp32 gate|up block, and
+// the rounding of fp32 rows to the dtype that feeds the next matrix product.  All arithmetic is fp32; the output
+// dtype is bf16 or fp32.  Beside the fp16 / bf16 row kernels of glue.cu (rmsnorm_kernel, silu_mul_kernel), which
+// keep a 16-bit residual.
+#include "../../include/b200_vllm.h"
+#include "seqmix.cuh"
+
+namespace b200 {
+using namespace seqmix;
+
+template <typename T>
+__global__ void embed_f32_kernel(float* __restrict__ x, const T* __restrict__ table, const uint32_t* __restrict__ ids,
+                                 int width, int vocab) {
+  const int t = blockIdx.x;
+  uint32_t id = ids[t];
+  if (id >= static_cast<uint32_t>(vocab)) id = 0;
+  const T* row = table + static_cast<size_t>(id) * width;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) x[static_cast<size_t>(t) * width + d] = ld(row + d);
+}
+
+// out[r] = x[row(r)] / sqrt(mean(x^2) + eps) * (w_offset + w); rows == nullptr: row(r) = r
+template <typename T>
+__global__ void resid_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                                     int width, float eps, float w_offset, const uint32_t* __restrict__ rows) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const float* xr = x + static_cast<size_t>(rows ? rows[r] : r) * width;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) ss += xr[d] * xr[d];
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(width) + eps);
+  for (int d = threadIdx.x; d < width; d += blockDim.x)
+    st(out + static_cast<size_t>(r) * width + d, xr[d] * inv * (w_offset + w[d]));
+}
+
+// One block per (token, group of `group` channels).  gate_first: u = y * silu(g), out = u / rms(u) * w;
+// otherwise out = y / rms(y) * w * silu(g).  w is indexed by (channel % w_period).
+template <typename T>
+__global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __restrict__ y, int ldy,
+                                        const float* __restrict__ gate, int ldg, const float* __restrict__ w,
+                                        int w_period, int C, int group, float eps, int gate_first) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, g0 = blockIdx.y * group;
+  const float* yr = y + static_cast<size_t>(t) * ldy + g0;
+  const float* gr = gate + static_cast<size_t>(t) * ldg + g0;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < group; d += blockDim.x) {
+    const float u = gate_first ? yr[d] * silu_exact(gr[d]) : yr[d];
+    ss += u * u;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(group) + eps);
+  for (int d = threadIdx.x; d < group; d += blockDim.x) {
+    const float s = silu_exact(gr[d]);
+    const float wv = w[(g0 + d) % w_period];
+    const float v = gate_first ? yr[d] * s * inv * wv : yr[d] * inv * wv * s;
+    st(out + static_cast<size_t>(t) * C + g0 + d, v);
+  }
+}
+
+template <typename T>
+__global__ void cast_rows_kernel(T* __restrict__ out, const float* __restrict__ in, int ld_in, int n, size_t total) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = i / n, d = i % n;
+    st(out + i, in[t * ld_in + d]);
+  }
+}
+
+template <typename T>
+__global__ void silu_mul_f32_kernel(T* __restrict__ out, const float* __restrict__ gu, int ff, size_t total) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = i / ff, d = i % ff;
+    st(out + i, silu_exact(gu[t * 2 * ff + d]) * gu[t * 2 * ff + ff + d]);
+  }
+}
+
+static int flat_grid(size_t total) {
+  const size_t b = (total + 255) / 256;
+  return static_cast<int>(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
+}
+
+void launch_embed_f32(float* x, const void* table, const uint32_t* ids, int T, int width, int vocab, int dt,
+                      cudaStream_t st_) {
+  if (T <= 0) return;
+  if (dt)
+    embed_f32_kernel<float><<<T, 256, 0, st_>>>(x, (const float*)table, ids, width, vocab);
+  else
+    embed_f32_kernel<__nv_bfloat16><<<T, 256, 0, st_>>>(x, (const __nv_bfloat16*)table, ids, width, vocab);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_resid_rmsnorm(void* out, const float* x, const float* w, int T, int width, float eps, float w_offset,
+                          const uint32_t* rows, int dt, cudaStream_t st_) {
+  if (T <= 0) return;
+  if (dt)
+    resid_rmsnorm_kernel<float><<<T, 256, 0, st_>>>((float*)out, x, w, width, eps, w_offset, rows);
+  else
+    resid_rmsnorm_kernel<__nv_bfloat16><<<T, 256, 0, st_>>>((__nv_bfloat16*)out, x, w, width, eps, w_offset, rows);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_gated_group_norm(void* out, const float* y, int ldy, const float* gate, int ldg, const float* w,
+                             int w_period, int T, int C, int group, float eps, int gate_first, int dt,
+                             cudaStream_t st_) {
+  if (T <= 0) return;
+  const dim3 grid(T, C / group);
+  const int threads = group >= 256 ? 256 : (group >= 128 ? 128 : 64);
+  if (dt)
+    gated_group_norm_kernel<float><<<grid, threads, 0, st_>>>((float*)out, y, ldy, gate, ldg, w, w_period, C, group,
+                                                              eps, gate_first);
+  else
+    gated_group_norm_kernel<__nv_bfloat16><<<grid, threads, 0, st_>>>((__nv_bfloat16*)out, y, ldy, gate, ldg, w,
+                                                                      w_period, C, group, eps, gate_first);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_cast_rows(void* out, const float* in, int ld_in, int T, int n, int dt, cudaStream_t st_) {
+  const size_t total = static_cast<size_t>(T) * n;
+  if (total == 0) return;
+  if (dt)
+    cast_rows_kernel<float><<<flat_grid(total), 256, 0, st_>>>((float*)out, in, ld_in, n, total);
+  else
+    cast_rows_kernel<__nv_bfloat16><<<flat_grid(total), 256, 0, st_>>>((__nv_bfloat16*)out, in, ld_in, n, total);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_silu_mul_f32(void* out, const float* gate_up, int T, int ff, int dt, cudaStream_t st_) {
+  const size_t total = static_cast<size_t>(T) * ff;
+  if (total == 0) return;
+  if (dt)
+    silu_mul_f32_kernel<float><<<flat_grid(total), 256, 0, st_>>>((float*)out, gate_up, ff, total);
+  else
+    silu_mul_f32_kernel<__nv_bfloat16><<<flat_grid(total), 256, 0, st_>>>((__nv_bfloat16*)out, gate_up, ff, total);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+}  // namespace b200
+
+extern "C" {
+// RMS norm of an fp32 residual stream: out[r] (bf16 when dt == 0, fp32 when dt == 1) = x[r] / sqrt(mean(x[r]^2) + eps)
+// * (w_offset + w); w fp32 [width]; w_offset = 1 for weights stored around zero, 0 for plain weights.
+void b200_resid_rmsnorm(void* out, const float* x, const float* w, int32_t num_tokens, int32_t width, float eps,
+                        float w_offset, int32_t dt, int64_t stream) {
+  B200_CHECK_ARG(out && x && w && width > 0 && (dt == 0 || dt == 1), "resid_rmsnorm: bad arguments");
+  b200::launch_resid_rmsnorm(out, x, w, num_tokens, width, eps, w_offset, nullptr, dt,
+                             reinterpret_cast<cudaStream_t>(stream));
+}
+// Grouped RMS norm with a SiLU gate over fp32 rows y [T, C] (row stride ldy), gate [T, C] (row stride ldg); groups of
+// `group` consecutive channels are normalised separately; w fp32 is indexed by channel % w_period (a per-head weight
+// shared by all heads has w_period = group).  gate_first != 0: norm(y * silu(gate)) * w; else norm(y) * w * silu(gate).
+void b200_gated_group_norm(void* out, const float* y, int32_t ldy, const float* gate, int32_t ldg, const float* w,
+                           int32_t w_period, int32_t num_tokens, int32_t channels, int32_t group, float eps,
+                           int32_t gate_first, int32_t dt, int64_t stream) {
+  B200_CHECK_ARG(out && y && gate && w && group > 0 && channels % group == 0 && w_period > 0 && (dt == 0 || dt == 1),
+                 "gated_group_norm: bad arguments");
+  b200::launch_gated_group_norm(out, y, ldy, gate, ldg, w, w_period, num_tokens, channels, group, eps, gate_first, dt,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+}

@@ -211,6 +211,62 @@ class Scheduler:
         return out
 
 
+    # ---- recurrent-state slots, host-driven (streamed) sequences and ragged steps
+    def enable_state_slots(self, n):
+        rc = self._l.b200_scheduler_enable_state_slots(self._h, int(n))
+        if rc < 0:
+            raise _lib.B200Error("enable_state_slots: needs a positive count and an idle scheduler")
+        return rc
+
+    @property
+    def num_free_state_slots(self):
+        return self._l.b200_scheduler_num_free_state_slots(self._h)
+
+    def state_slot(self, i):
+        return self._l.b200_scheduler_seq_state_slot(self._h, int(i))
+
+    def open(self) -> int:
+        """A sequence the host drives itself (feed / prepare_ragged / close); -1 when no state slot is free."""
+        return self._l.b200_scheduler_open(self._h)
+
+    def feed(self, seq_id, token_ids) -> int:
+        """Append tokens to a streamed sequence and grow its block table; 0, -1 out of blocks (nothing taken), -2."""
+        arr = np.ascontiguousarray(token_ids, dtype=np.uint32)
+        return self._l.b200_scheduler_feed(self._h, int(seq_id), arr.ctypes.data, len(arr))
+
+    def close(self, seq_id) -> int:
+        return self._l.b200_scheduler_close(self._h, int(seq_id))
+
+    def running_index(self, seq_id) -> int:
+        return self._l.b200_scheduler_running_index(self._h, int(seq_id))
+
+    def prepare_ragged(self, ids, counts=None, mode=2, token_cap=1 << 16, max_blocks_cap=1024, pinned=None):
+        """Step metadata of any mix of running sequences (b200_prepare_ragged): mode 0 a scheduled prefill chunk,
+        1 decode (the last token), 2 streamed (everything fed since the last step; commits)."""
+        n = len(ids)
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        cn = None if counts is None else np.ascontiguousarray(counts, dtype=np.int32)
+        if pinned is None:
+            bufs = dict(input_ids=np.zeros(token_cap, np.uint32), positions=np.zeros(token_cap, np.int64),
+                        slot_mapping=np.zeros(token_cap, np.int64), cu_seqlens_q=np.zeros(n + 1, np.uint32),
+                        context_lens=np.zeros(n, np.uint32), block_tables=np.zeros(n * max_blocks_cap, np.uint32),
+                        state_slots=np.zeros(n, np.int32))
+        else:
+            bufs = pinned
+            token_cap = min(token_cap, len(bufs["input_ids"]))
+            if n + 1 > len(bufs["cu_seqlens_q"]) or n * max_blocks_cap > len(bufs["block_tables"]):
+                raise _lib.B200Error("prepare_ragged: more sequences than the staging buffers hold")
+        T = self._l.b200_prepare_ragged(self._h, a.ctypes.data, None if cn is None else cn.ctypes.data, n, int(mode),
+                                        token_cap, max_blocks_cap, bufs["input_ids"].ctypes.data,
+                                        bufs["positions"].ctypes.data, bufs["slot_mapping"].ctypes.data,
+                                        bufs["cu_seqlens_q"].ctypes.data, bufs["context_lens"].ctypes.data,
+                                        bufs["block_tables"].ctypes.data, bufs["state_slots"].ctypes.data)
+        if T < 0:
+            raise _lib.B200Error("prepare_ragged: " + ("capacity exceeded" if T == -1 else "bad index or count"))
+        out = dict(bufs)
+        out.update(num_seqs=n, num_tokens=T, max_blocks=max_blocks_cap)
+        return out
+
     # ---- RunPrefill frames (runner/mod.rs:178): the engine side frames its scheduled sequences, a runner side loads them
     def frame_run_prefill(self, ids, is_prefill=True) -> bytes:
         a = np.ascontiguousarray(ids, dtype=np.int32)
@@ -479,11 +535,22 @@ class LLMEngine:
                  chunk_size=8192, prefix_cache=False, prefix_cache_max_tokens=None, native_step=True,
                  max_num_batched_tokens=0, seed=None, num_cpu_blocks=0):
         self.runner = runner
+        # a runner of the hybrid family (vllm_rs_b200/hybrid.py) takes ragged steps and needs a state slot per sequence
+        self.ragged = hasattr(runner, "step")
+        if self.ragged:
+            native_step = False
+            if max(max_num_seqs, 5) > runner.cfg.max_seqs:
+                raise ValueError(f"runner max_seqs {runner.cfg.max_seqs} < max(max_num_seqs, 5) = {max(max_num_seqs, 5)}")
+            if prefix_cache or num_cpu_blocks:
+                raise ValueError("recurrent state is neither prefix-cached nor swapped: run hybrid models without both")
+            chunk_size = min(chunk_size, runner.cfg.max_tokens)
         # the scheduler hands out up to max(max_num_seqs, 5) sequences per step (scheduler.rs:44); the runner
         # must be able to take such a decode batch, and one chunk of one sequence as a prefill step
-        if max(max_num_seqs, 5) > runner.cfg.max_batch:
+        elif max(max_num_seqs, 5) > runner.cfg.max_batch:
             raise ValueError(f"runner max_batch {runner.cfg.max_batch} < max(max_num_seqs, 5) = {max(max_num_seqs, 5)}")
         self.sched = Scheduler(num_blocks, 64, max_num_seqs, max_num_batched_tokens, chunk_size, eos_token_ids)
+        if self.ragged:
+            self.sched.enable_state_slots(runner.cfg.num_state_slots)
         if prefix_cache:                    # EngineConfig.prefix_cache / prefix_cache_max_tokens
             self.sched.enable_prefix_cache(prefix_cache_max_tokens)
         # native_step: schedule -> prepare_decode -> run -> postprocess of a decode batch is ONE C call
@@ -597,7 +664,9 @@ class LLMEngine:
             self._drain_swaps()
         if not ids:
             return False
-        if is_prefill:
+        if self.ragged:
+            self._ragged_step(ids, is_prefill)
+        elif is_prefill:
             parts = []
             self.last_kind = "prefill"
             for sub in self._prefill_batches(ids):
@@ -625,6 +694,41 @@ class LLMEngine:
             self.sched.postprocess(ids, toks)
         self.sched.clear_finished()
         return True
+
+    def _ragged_step(self, ids, is_prefill):
+        """A scheduled batch on a ragged-step runner: prefill chunks and decode tokens are the same call; when the
+        chunks of a batch exceed the runner's rows per step it is cut at sequence boundaries."""
+        r = self.runner
+        self.last_kind = "prefill" if is_prefill else "decode"
+        toks = np.zeros(len(ids), np.uint32)
+        start = 0
+        while start < len(ids):
+            end, rows = start, 0
+            while end < len(ids):
+                info = self.sched.seq_info(ids[end])
+                c = min(self.sched.chunk_size, info["len"] - info["num_cached_tokens"]) if is_prefill else 1
+                if end > start and (rows + c > r.cfg.max_tokens or end - start >= r.cfg.max_seqs):
+                    break
+                rows += c
+                end += 1
+            meta = self.sched.prepare_ragged(ids[start:end], None, 0 if is_prefill else 1, r.cfg.max_tokens,
+                                             self.max_blocks, pinned=r.pinned)
+            if is_prefill:
+                self.last_prefill_tokens += meta["num_tokens"]
+            if self._rng:
+                r.set_step_seed(self._l.b200_rng_next_u64(self._rng))
+            last = meta["cu_seqlens_q"][1:end - start + 1].astype(np.int64) - 1
+            _, t = r.step(meta, last)
+            toks[start:end] = t
+            start = end
+        if is_prefill:
+            pos, fin = self.sched.filter_prefill_finished(ids)
+            sel = toks[pos] if len(pos) else toks[:0]
+        else:
+            fin, sel = ids, toks
+        for i, t in zip(fin, sel):
+            self.outputs[self.sched.seq_info(i)["id"]].append(int(t))
+        self.sched.postprocess(fin, sel)
 
     def run_to_completion(self, max_steps=100000):
         n = 0

@@ -294,3 +294,140 @@ def apply_penalties(logits, context, context_lens, frequency_penalty, presence_p
                                         float(frequency_penalty), float(presence_penalty), _stream())
     _lib.check()
     return logits
+
+
+def sampling_strategy(temperature=None, top_k=None, top_p=None):
+    """LogitsProcessor::get_strategy (logits_processor.rs:48-70): (strategy, k, p, t) for the runners' set_sampling."""
+    import ctypes as C
+    k, p, t = C.c_int32(0), C.c_float(1.0), C.c_float(1.0)
+    s = _lib.lib().b200_sampling_strategy(int(temperature is not None), float(temperature or 0.0),
+                                          int(top_k is not None), int(top_k or 0), int(top_p is not None),
+                                          float(top_p or 0.0), C.byref(k), C.byref(p), C.byref(t))
+    return s, k.value, p.value, t.value
+
+
+# ------------------------------------------------------------------ mixers of the fp32-residual hybrid decoders
+# Ragged steps: cu_seqlens_q i32 [B + 1], context_lens i32 [B] (length after the step), block_tables i32 [B, max_blocks],
+# state_slots i32 [B].  `dtype` of an output that feeds a matrix product: torch.bfloat16 or torch.float32.
+def _dt(dtype) -> int:
+    if dtype == torch.bfloat16:
+        return 0
+    if dtype == torch.float32:
+        return 1
+    raise TypeError("operand dtype must be bfloat16 or float32")
+
+
+def resid_rmsnorm(x, w, eps, w_offset=0.0, dtype=torch.bfloat16):
+    """RMS norm of an fp32 stream x [T, D] with fp32 weight (w_offset + w)."""
+    _cuda(x, w)
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _lib.lib().b200_resid_rmsnorm(_p(out), _p(x), _p(w), x.shape[0], x.shape[1], float(eps), float(w_offset),
+                                  _dt(dtype), _stream())
+    _lib.check()
+    return out
+
+
+def gated_group_norm(y, gate, w, group, eps, gate_first, dtype=torch.bfloat16):
+    """y, gate fp32 [T, C]; groups of `group` channels; w fp32 [C] or [group] (shared by the groups)."""
+    _cuda(y, gate, w)
+    T, Cn = y.shape
+    out = torch.empty(T, Cn, dtype=dtype, device=y.device)
+    _lib.lib().b200_gated_group_norm(_p(out), _p(y), Cn, _p(gate), Cn, _p(w), w.numel(), T, Cn, int(group), float(eps),
+                                     int(bool(gate_first)), _dt(dtype), _stream())
+    _lib.check()
+    return out
+
+
+def latent_prep(qc, cache, latent_norm_w, rot_freq, rot_mag, positions, slot_mapping, *, heads, dim, rot_dim, rot_dims,
+                kv_rank, eps):
+    """Returns (q_plain [T, heads, dim] in the cache dtype, q_full fp32 [T, heads, kv_rank + rot_dim] with the
+    rotated parts filled and the first kv_rank entries of every head left for the absorbed query)."""
+    _cuda(qc, cache, latent_norm_w, rot_freq, positions, slot_mapping)
+    T = qc.shape[0]
+    q_plain = torch.empty(T, heads, dim, dtype=cache.dtype, device=qc.device)
+    q_full = torch.zeros(T, heads, kv_rank + rot_dim, dtype=torch.float32, device=qc.device)
+    _lib.lib().b200_latent_prep(_p(qc), qc.shape[1], _p(q_plain), _p(q_full), _p(cache), _p(latent_norm_w),
+                                _p(rot_freq), float(rot_mag), _p(positions), _p(slot_mapping), T, heads, dim, rot_dim,
+                                rot_dims, kv_rank, float(eps), _dt(cache.dtype), _stream())
+    _lib.check()
+    return q_plain, q_full
+
+
+def latent_attn(q_full, cache, sink, cu_seqlens_q, context_lens, block_tables, *, kv_rank, rot_dim, window, scale):
+    """Attention-weighted latents [T, heads, kv_rank] in the cache dtype."""
+    _cuda(q_full, cache, sink, cu_seqlens_q, context_lens, block_tables)
+    T, H, _ = q_full.shape
+    out = torch.empty(T, H, kv_rank, dtype=cache.dtype, device=q_full.device)
+    _lib.lib().b200_latent_attn(_p(out), _p(q_full), _p(cache), _p(sink), _p(cu_seqlens_q), _p(context_lens),
+                                _p(block_tables), block_tables.shape[1], context_lens.shape[0], T, H, kv_rank, rot_dim,
+                                int(window), float(scale), _dt(cache.dtype), _stream())
+    _lib.check()
+    return out
+
+
+def short_conv_silu(x, taps_w, bias, state, state_slots, cu_seqlens_q, context_lens):
+    """x fp32 [T, C] -> silu(causal conv) fp32 [T, C]; state fp32 [slots, taps - 1, C] is read and updated."""
+    _cuda(x, taps_w, bias, state, state_slots, cu_seqlens_q, context_lens)
+    out = torch.empty_like(x)
+    _lib.lib().b200_short_conv_silu(_p(out), x.shape[1], _p(x), x.shape[1], _p(taps_w), _p(bias), _p(state),
+                                    _p(state_slots), _p(cu_seqlens_q), _p(context_lens), context_lens.shape[0],
+                                    x.shape[1], taps_w.shape[1], _stream())
+    _lib.check()
+    return out
+
+
+def delta_rule(q, k, v, b_raw, a_raw, a_log, dt_bias, state, state_slots, cu_seqlens_q, context_lens):
+    """q, k fp32 [T, kv_heads, dim], v [T, heads, vdim], b_raw / a_raw [T, heads] -> o fp32 [T, heads, vdim]."""
+    T, Hk, dk = q.shape
+    H, dv = v.shape[1], v.shape[2]
+    row = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1), b_raw, a_raw], 1).contiguous()
+    _cuda(row, a_log, dt_bias, state, state_slots, cu_seqlens_q, context_lens)
+    out = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
+    ld, e = row.shape[1], 4
+    base = row.data_ptr()
+    _lib.lib().b200_delta_rule(_p(out), base, base + Hk * dk * e, base + 2 * Hk * dk * e, ld,
+                               base + (2 * Hk * dk + H * dv) * e, base + (2 * Hk * dk + H * dv + H) * e, ld, _p(a_log),
+                               _p(dt_bias), _p(state), _p(state_slots), _p(cu_seqlens_q), _p(context_lens),
+                               context_lens.shape[0], H, Hk, dk, dv, _stream())
+    _lib.check()
+    return out
+
+
+def ssd_scan(x, Bm, Cm, dt_raw, a_log, dt_bias, d_skip, state, state_slots, cu_seqlens_q, context_lens):
+    """x fp32 [T, heads, vdim], Bm / Cm [T, groups, nstate], dt_raw [T, heads] -> y fp32 [T, heads, vdim]."""
+    T, H, P = x.shape
+    G, N = Bm.shape[1], Bm.shape[2]
+    row = torch.cat([x.reshape(T, -1), Bm.reshape(T, -1), Cm.reshape(T, -1), dt_raw], 1).contiguous()
+    _cuda(row, a_log, dt_bias, d_skip, state, state_slots, cu_seqlens_q, context_lens)
+    out = torch.empty(T, H, P, dtype=torch.float32, device=x.device)
+    ld, e, base = row.shape[1], 4, row.data_ptr()
+    _lib.lib().b200_ssd_scan(_p(out), base, base + H * P * e, base + (H * P + G * N) * e, ld,
+                             base + (H * P + 2 * G * N) * e, ld, _p(a_log), _p(dt_bias), _p(d_skip), _p(state),
+                             _p(state_slots), _p(cu_seqlens_q), _p(context_lens), context_lens.shape[0], H, G, N, P,
+                             _stream())
+    _lib.check()
+    return out
+
+
+def moe_route(logits, top, scale):
+    _cuda(logits)
+    T, E = logits.shape
+    idx = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    _lib.lib().b200_moe_route(_p(logits), T, E, int(top), float(scale), _p(idx), _p(w), _stream())
+    _lib.check()
+    return idx, w
+
+
+def moe_experts(x, h, top_idx, top_w, w_gate_up, w_down):
+    """x fp32 [T, D] += routed experts of h [T, D]; w_gate_up [E, 2 F, D], w_down [E, D, F] in h's dtype."""
+    _cuda(x, h, top_idx, top_w, w_gate_up, w_down)
+    T, D = x.shape
+    E, F2, _ = w_gate_up.shape
+    top = top_idx.shape[1]
+    nbytes = _lib.lib().b200_moe_workspace_bytes(T, E, top, D, F2 // 2)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    _lib.lib().b200_moe_experts(_p(x), _p(h), _p(top_idx), _p(top_w), _p(w_gate_up), _p(w_down), T, E, top, D, F2 // 2,
+                                _dt(h.dtype), _p(ws), _stream())
+    _lib.check()
+    return x
