@@ -645,14 +645,18 @@ int32_t b200_scheduler_schedule(b200_scheduler* s, int32_t* indices, int32_t cap
   const size_t pre_existing_running = s->running.size();
   const size_t max_seqs_limit = std::max(s->max_num_seqs, kMinNumScheduledReqs);
   // ---- prefill phase (scheduler.rs:232-283)
+  std::vector<Sequence> deferred;      // waiting for a state slot; sequences behind them that hold one go on
   while (!s->waiting.empty()) {
     Sequence seq = std::move(s->waiting.front());
     s->waiting.pop_front();
+    if (s->state_slots_on && seq.state_slot < 0 && s->free_state_slots.empty()) {
+      deferred.push_back(std::move(seq));
+      continue;
+    }
     const size_t effective = std::min(s->chunk_size, seq.len() - seq.num_cached_tokens);
     if (s->running.size() >= max_seqs_limit || scheduled.size() >= max_seqs_limit ||
         num_tokens + effective >= s->max_num_batched_tokens - 1 ||
         (seq.block_table.empty() && !s->bm.can_allocate(seq)) ||
-        (s->state_slots_on && seq.state_slot < 0 && s->free_state_slots.empty()) ||
         (s->is_last_prefill && pre_existing_running > 0)) {
       s->waiting.push_front(std::move(seq));
       break;
@@ -672,6 +676,7 @@ int32_t b200_scheduler_schedule(b200_scheduler* s, int32_t* indices, int32_t cap
     s->running.push_back(std::move(seq));
     scheduled.push_back(s->running.size() - 1);
   }
+  for (auto it = deferred.rbegin(); it != deferred.rend(); ++it) s->waiting.push_front(std::move(*it));
   if (!scheduled.empty()) {
     s->is_last_prefill = true;
     *is_prefill = 1;
