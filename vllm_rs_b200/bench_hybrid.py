@@ -81,6 +81,11 @@ def random_tensors(cfg, seed=0):
     return out
 
 
+def _say(msg):
+    import sys
+    print(f"[bench_hybrid] {msg}", file=sys.stderr, flush=True)
+
+
 def _time(fn, reps, warm=3):
     for _ in range(warm):
         fn()
@@ -121,6 +126,7 @@ def kernel_table(size, prefill, batch, ctx, peaks):
     rows = []
 
     def add(name, phase, ms, flops=0.0, nbytes=0.0, bound="hbm", note=""):
+        _say(f"{name} {phase}: {ms:.3f} ms")
         ach_f, ach_b = flops / (ms * 1e-3), nbytes / (ms * 1e-3)
         frac = {"hbm": ach_b / hbm, "tensor": ach_f / tc, "fp32": ach_f / fma}[bound]
         rows.append(dict(kernel=name, phase=phase, ms=round(ms, 4), tflops=round(ach_f / 1e12, 3),
@@ -206,14 +212,18 @@ def run(size="w2048", layers=4, prefill=4096, batch=32, ctx=2048, reps=5):
     r = models.build_runner(cfg, random_tensors(cfg), dtype=torch.bfloat16, device="cuda", num_blocks=batch * nblk,
                             max_blocks_per_seq=nblk, max_seqs=batch, max_tokens=max(prefill, batch),
                             num_state_slots=batch)
+    _say("hybrid runner built")
     for c in r.kv_cache.values():
         c.normal_(std=0.3)
     mp = _meta(1, prefill, prefill, nblk, s["vocab"])
-    ms = _time(lambda: r.step(mp, [prefill - 1]), reps, warm=2)
+    ms = _time(lambda: r.step(mp, [prefill - 1]), 1, warm=1)
+    _say(f"first prefill steps: {ms:.2f} ms")
+    ms = _time(lambda: r.step(mp, [prefill - 1]), reps, warm=1)
     res["fidasun"] = {"prefill_ms": ms, "prefill_tok_s": prefill * 1e3 / ms, "launches": int(r.launches_per_step)}
     md = _meta(batch, 1, ctx, nblk, s["vocab"])
     ms = _time(lambda: r.step(md, list(range(batch))), reps * 4, warm=3)
     res["fidasun"].update(decode_ms=ms, decode_tok_s=batch * 1e3 / ms)
+    _say(f"fidasun: {res['fidasun']}")
     del r
     torch.cuda.empty_cache()
     # ---- the dense fp16 LLaMA plan at equal width / depth / active feed-forward size
@@ -234,6 +244,7 @@ def run(size="w2048", layers=4, prefill=4096, batch=32, ctx=2048, reps=5):
     bt, cl = t(md["block_tables"].reshape(batch, nblk), np.int32), t(md["context_lens"], np.int32)
     ms = _time(lambda: lr.decode_device(ids, pos, slot, bt, cl, want_logits=False), reps * 4, warm=3)
     res["llama_fp16"].update(decode_ms=ms, decode_tok_s=batch * 1e3 / ms, launches=int(lr.launches_per_step))
+    _say(f"llama fp16: {res['llama_fp16']}")
     del lr
     torch.cuda.empty_cache()
     res["kernels"] = kernel_table(size, prefill, batch, ctx, peaks)
