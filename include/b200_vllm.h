@@ -688,11 +688,14 @@ void b200_latent_prep(const float* qc, int32_t ldq, void* q_plain, float* q_full
                       const int64_t* slot_mapping, int32_t num_tokens, int32_t heads, int32_t dim, int32_t rot_dim,
                       int32_t rot_dims, int32_t kv_rank, float eps, int32_t dt, int64_t stream);
 /* out [T, heads, kv_rank] (dtype dt) = softmax-weighted sum of cached latents; sink fp32 [heads] or NULL;
- * window <= 0: full causal context.  cache [num_blocks, 64, kv_rank + rot_dim].                                   */
+ * window <= 0: full causal context.  cache [num_blocks, 64, kv_rank + rot_dim].  workspace (may be NULL):
+ * b200_latent_attn_workspace_bytes() bytes; with it, steps of few token rows split each row's keys over several
+ * blocks and merge the parts (the result is the same softmax, summed in another order).                           */
 void b200_latent_attn(void* out, const float* q_full, const void* cache, const float* sink,
                       const uint32_t* cu_seqlens_q, const uint32_t* context_lens, const uint32_t* block_tables,
                       int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens, int32_t heads, int32_t kv_rank,
-                      int32_t rot_dim, int32_t window, float scale, int32_t dt, int64_t stream);
+                      int32_t rot_dim, int32_t window, float scale, int32_t dt, void* workspace, int64_t stream);
+int64_t b200_latent_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_rank, int32_t window);
 /* Causal per-channel convolution + SiLU; state fp32 [slots, taps - 1, channels]; taps_w fp32 [channels, taps] (last
  * column = current token), bias fp32 [channels] or NULL.  out may alias x.                                        */
 void b200_short_conv_silu(float* out, int32_t ldo, const float* x, int32_t ldx, const float* taps_w, const float* bias,

@@ -176,7 +176,8 @@ def test_delta_rule_and_ssd_ops_in_portions(lib):
 # ------------------------------------------------------------------ window and page edges, made to show
 @pytest.mark.parametrize("window", [0, 5, 64, 70, 130])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_latent_attention_sees_exactly_its_window(lib, window, dtype):
+@pytest.mark.parametrize("split", [True, False])
+def test_latent_attention_sees_exactly_its_window(lib, window, dtype, split):
     """Every cached latent is a distinct random vector and the query is made to score the EARLIEST visible key far
     above all others: the output must be the latent at the window's far edge, never the one just outside it; checked
     for prompt rows and for single decoded rows, with edges at page borders and far back, on a shuffled block table."""
@@ -202,7 +203,8 @@ def test_latent_attention_sees_exactly_its_window(lib, window, dtype):
         q = torch.zeros(T, H, R_)
         q[:, :, r:] = -4000.0 / dr                                     # prefers the earliest visible key
         out = ops.latent_attn(q.cuda().contiguous(), cache, torch.full((H,), -1e4, device="cuda"), _i32([0, T]),
-                              _i32([rows_pos[-1] + 1]), bt, kv_rank=r, rot_dim=dr, window=window, scale=1.0).float().cpu()
+                              _i32([rows_pos[-1] + 1]), bt, kv_rank=r, rot_dim=dr, window=window, scale=1.0,
+                              split=split).float().cpu()
         tol = 2e-3 if dtype == torch.float32 else 3e-2
         for i, p in enumerate(rows_pos):
             j = first_visible(p)
@@ -212,7 +214,7 @@ def test_latent_attention_sees_exactly_its_window(lib, window, dtype):
     # the sink takes its share: with a sink as large as the best score the output halves
     q = torch.zeros(1, H, R_)
     out = ops.latent_attn(q.cuda(), cache, torch.tensor([0.0, -1e4], device="cuda"), _i32([0, 1]), _i32([1]), bt,
-                          kv_rank=r, rot_dim=dr, window=window, scale=1.0).float().cpu()
+                          kv_rank=r, rot_dim=dr, window=window, scale=1.0, split=split).float().cpu()
     assert (out[0, 0] - 0.5 * lat[0].to(dtype).float()).abs().max() <= 2e-2
     assert (out[0, 1] - lat[0].to(dtype).float()).abs().max() <= 2e-2
 

@@ -39,6 +39,11 @@ bool gemm_f32out(const void* a, int lda, long long stride_a, const void* w, int 
     return false;
   }
   cublasSetStream(h, st);
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);       // setting the stream drops the user workspace: give it back (keeps the call capturable)
+    if (g_ws[dev]) cublasSetWorkspace(h, g_ws[dev], 32u << 20);
+  }
   const float alpha = 1.f;
   const cudaDataType_t in = dt ? CUDA_R_32F : CUDA_R_16BF;
   const cublasComputeType_t comp = dt ? CUBLAS_COMPUTE_32F_PEDANTIC : CUBLAS_COMPUTE_32F;

@@ -19,7 +19,10 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
+#include <map>
+#include <tuple>
 #include <vector>
 
 #include "../../../include/b200_vllm.h"
@@ -49,6 +52,8 @@ struct b200_hybrid {
   float* aux = nullptr;        // [T, max(heads (kv_rank + rot_dim), heads vdim)] fp32: q_full / scan output / expanded values
   void* opa = nullptr;         // [T, max(heads dim, heads vdim, 2 shared... )] operand dtype: q_plain, then the o-projection input
   void* lat = nullptr;         // [T, heads kv_rank] operand dtype: attention-weighted latents
+  void* attn_ws = nullptr;     // parts of split attention rows (steps of few token rows)
+  size_t attn_ws_rows = 0;     // token rows the parts are sized for
   float* rlog = nullptr;       // [T, experts]
   int32_t* top_idx = nullptr;
   float* top_w = nullptr;
@@ -67,7 +72,30 @@ struct b200_hybrid {
   bool samp_all = false;
   float samp_p = 1.f, samp_t = 1.f;
   int64_t launches = 0;
+  // CUDA graphs of small steps (decoding, short portions), keyed by the host-side sizes that are kernel arguments:
+  // (sequences, token rows, block-table width, output rows, ids wanted).  A shape is captured the second time it is
+  // seen (the first run warms up lazily created library state); the step's inputs live in the static staging buffers.
+  struct GraphEntry {
+    int seen = 0;
+    cudaGraphExec_t exec = nullptr;
+  };
+  std::map<std::tuple<int, int, int, int, int>, GraphEntry> graphs;
+  void drop_graphs() {
+    for (auto& g : graphs)
+      if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+    graphs.clear();
+  }
 };
+
+constexpr int kGraphMaxRows = 256;
+static bool graphs_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200_HYBRID_GRAPHS");      // 0: every step is launched directly (A/B arm)
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
 
 static int in_rows(const b200_hybrid_layer& l) {
   switch (l.mixer) {
@@ -80,13 +108,17 @@ static int in_rows(const b200_hybrid_layer& l) {
 static int64_t carve(b200_hybrid* r, uint8_t* base) {
   const b200_hybrid_config& c = r->cfg;
   const size_t T = c.max_tokens, es = c.dt ? 4 : 2;
-  size_t proj_n = 1, aux_n = 1, opa_n = 1, lat_n = 1, E = 1, top = 1, sh_n = 1, moe_bytes = 256;
+  size_t proj_n = 1, aux_n = 1, opa_n = 1, lat_n = 1, E = 1, top = 1, sh_n = 1, moe_bytes = 256, attn_bytes = 0;
+  // rows up to which a step may split its attention rows: beyond two blocks per SM a split is never chosen
+  r->attn_ws_rows = std::min<size_t>(T, 2 * static_cast<size_t>(sm_count()));
   for (const b200_hybrid_layer& l : r->layers) {
     proj_n = std::max<size_t>(proj_n, in_rows(l));
     if (l.mixer == B200_MIXER_LATENT_ATTN) {
       aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * std::max(l.kv_rank + l.rot_dim, l.vdim));
       opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * std::max(l.dim, l.vdim));
       lat_n = std::max<size_t>(lat_n, static_cast<size_t>(l.heads) * l.kv_rank);
+      for (size_t rows = 1; rows <= r->attn_ws_rows; ++rows)
+        attn_bytes = std::max(attn_bytes, latent_attn_workspace_bytes(static_cast<int>(rows), l.heads, l.kv_rank, l.window));
     } else {
       aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * l.vdim);
       opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * l.vdim);
@@ -110,6 +142,7 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
   r->aux = (float*)take(T * aux_n * 4);
   r->opa = take(T * opa_n * es);
   r->lat = take(T * lat_n * es);
+  r->attn_ws = attn_bytes ? take(attn_bytes) : nullptr;
   r->rlog = (float*)take(T * E * 4);
   r->top_idx = (int32_t*)take(T * top * 4);
   r->top_w = (float*)take(T * top * 4);
@@ -146,7 +179,11 @@ b200_hybrid* b200_hybrid_new(const b200_hybrid_config* cfg) {
   return r;
 }
 
-void b200_hybrid_free(b200_hybrid* r) { delete r; }
+void b200_hybrid_free(b200_hybrid* r) {
+  if (!r) return;
+  r->drop_graphs();
+  delete r;
+}
 
 void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_layer* l) {
   if (layer < 0 || layer >= r->cfg.num_layers || !l) {
@@ -198,9 +235,13 @@ void b200_hybrid_set_workspace(b200_hybrid* r, void* workspace, int64_t bytes) {
   r->ws = base;
 }
 
-void b200_hybrid_set_layer_trace(b200_hybrid* r, float* buf) { r->trace = buf; }
+void b200_hybrid_set_layer_trace(b200_hybrid* r, float* buf) {
+  r->trace = buf;
+  r->drop_graphs();
+}
 
 int32_t b200_hybrid_set_sampling(b200_hybrid* r, int32_t strategy, int32_t k, float p, float t) {
+  r->drop_graphs();              // k, p and t are kernel arguments of the captured sampler launch
   if (strategy == 0) {
     r->samp_all = false; r->samp_k = 0; r->samp_p = 1.f; r->samp_t = 1.f;
     return 0;
@@ -239,7 +280,8 @@ static void mixer_latent(b200_hybrid* r, const b200_hybrid_layer& l, const int64
   else
     cudaMemsetAsync(r->aux, 0, static_cast<size_t>(T) * H * R * 4, st);   // (rotated parts are rewritten by prep; dim == 0 is rejected upstream)
   launch_latent_attn(r->lat, r->aux, l.kv_cache, (const float*)l.sink, cu, ctx, bt, max_blocks, B, T, H, l.kv_rank,
-                     l.rot_dim, l.window, l.scale, c.dt, st);
+                     l.rot_dim, l.window, l.scale, c.dt,
+                     static_cast<size_t>(T) <= r->attn_ws_rows ? r->attn_ws : nullptr, st);
   // v[t, h, :] = lat[t, h, :] W_uv[h]^T  (W_uv[h] is [vdim, kv_rank])
   gemm_f32out(r->lat, H * l.kv_rank, l.kv_rank, l.w_uv, l.kv_rank, static_cast<long long>(l.vdim) * l.kv_rank, r->aux,
               H * l.vdim, l.vdim, T, l.vdim, l.kv_rank, H, 0.f, 0, c.dt, st);
@@ -378,8 +420,35 @@ int32_t b200_hybrid_step_host(b200_hybrid* r, const uint32_t* input_ids, const i
   cudaMemcpyAsync(r->s_state, state_slots, B * 4, H2D, st);
   cudaMemcpyAsync(r->s_bt, block_tables, static_cast<size_t>(B) * max_blocks * 4, H2D, st);
   if (num_out > 0) cudaMemcpyAsync(r->s_rows, out_rows, num_out * 4, H2D, st);
-  b200_hybrid_step(r, r->s_ids, r->s_pos, r->s_slot, r->s_cu, r->s_ctx, r->s_bt, r->s_state, r->s_rows, B, T,
-                   max_blocks, num_out, nullptr, out_ids_host ? r->s_out : nullptr, stream);
+  auto run = [&]() {
+    b200_hybrid_step(r, r->s_ids, r->s_pos, r->s_slot, r->s_cu, r->s_ctx, r->s_bt, r->s_state, r->s_rows, B, T,
+                     max_blocks, num_out, nullptr, out_ids_host ? r->s_out : nullptr, stream);
+  };
+  bool done = false;
+  if (graphs_enabled() && !r->trace && T <= kGraphMaxRows && st != nullptr) {      // the legacy stream cannot capture
+    if (r->graphs.size() > 512) r->drop_graphs();
+    auto& g = r->graphs[std::make_tuple(B, T, max_blocks, num_out, out_ids_host ? 1 : 0)];
+    if (!g.exec && g.seen++ >= 1 && !b200_last_error()) {
+      cudaGraph_t graph = nullptr;
+      if (cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed) == cudaSuccess) {
+        const int64_t launches = r->launches;
+        run();
+        if (cudaStreamEndCapture(st, &graph) == cudaSuccess && graph && !b200_last_error())
+          if (cudaGraphInstantiate(&g.exec, graph, 0) != cudaSuccess) g.exec = nullptr;
+        if (graph) cudaGraphDestroy(graph);
+        if (!g.exec) {
+          cudaGetLastError();
+          g.seen = -(1 << 30);          // this shape stays on direct launches
+        }
+        r->launches = launches;
+      }
+    }
+    if (g.exec) {
+      cudaGraphLaunch(g.exec, st);
+      done = true;
+    }
+  }
+  if (!done) run();
   if (num_out > 0 && logits_host)
     cudaMemcpyAsync(logits_host, r->logits, static_cast<size_t>(num_out) * c.vocab * 4, cudaMemcpyDeviceToHost, st);
   if (num_out > 0 && out_ids_host) cudaMemcpyAsync(out_ids_host, r->s_out, num_out * 4, cudaMemcpyDeviceToHost, st);

@@ -17,6 +17,8 @@
 // part and of the shared key part as interleaved pairs (2i, 2i+1) by the angle position * freq[i] (angles in double,
 // cos / sin scaled by rot_mag), writes the cache row at the token's slot, and splits the queries.
 #include "../../include/b200_vllm.h"
+#include <algorithm>
+
 #include "seqmix.cuh"
 
 namespace b200 {
@@ -90,7 +92,8 @@ __global__ void latent_attn_kernel(T* __restrict__ out, const float* __restrict_
                                    const float* __restrict__ sink, const uint32_t* __restrict__ cu,
                                    const uint32_t* __restrict__ ctx, const uint32_t* __restrict__ block_tables,
                                    int max_blocks, int num_seqs, int heads, int kv_rank, int rot_dim, int window,
-                                   float scale, int key_tile) {
+                                   float scale, int key_tile, int nsplit, float* __restrict__ part_o,
+                                   float* __restrict__ part_ml) {
   extern __shared__ float sm[];
   const int R = kv_rank + rot_dim, Rp = R | 1;        // odd row pitch: a lane per key reads conflict-free
   const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -110,13 +113,18 @@ __global__ void latent_attn_kernel(T* __restrict__ out, const float* __restrict_
     for (int d = lane; d < kv_rank; d += 32) os[warp * kv_rank + d] = 0.f;
   }
   float m = -1e30f, l = 0.f;
-  if (live && sink) {
+  if (live && sink && nsplit == 1) {       // split runs add the sink when the parts are merged
     m = sink[h];
     l = 1.f;
   }
   const uint32_t* bt = block_tables + static_cast<size_t>(b) * max_blocks;
-  for (int j0 = lo; j0 <= pos; j0 += key_tile) {
-    const int nk = min(key_tile, pos - j0 + 1);
+  // blockIdx.z owns a contiguous run of key tiles (nsplit == 1: all of them)
+  const int ntiles = (pos - lo + key_tile) / key_tile;
+  const int per = (ntiles + nsplit - 1) / nsplit;
+  const int first = lo + static_cast<int>(blockIdx.z) * per * key_tile;
+  const int last = min(pos, first + per * key_tile - 1);
+  for (int j0 = first; j0 <= last; j0 += key_tile) {
+    const int nk = min(key_tile, last - j0 + 1);
     __syncthreads();
     for (int e = threadIdx.x; e < nk * R; e += blockDim.x) {
       const int k = e / R, d = e % R, j = j0 + k;
@@ -154,10 +162,37 @@ __global__ void latent_attn_kernel(T* __restrict__ out, const float* __restrict_
       }
     }
   }
-  if (live) {
+  if (live && nsplit == 1) {
     const float inv = l > 0.f ? 1.f / l : 0.f;
     T* o = out + (static_cast<size_t>(t) * heads + h) * kv_rank;
     for (int d = lane; d < kv_rank; d += 32) st(o + d, os[warp * kv_rank + d] * inv);
+  } else if (live) {
+    const size_t pi = (static_cast<size_t>(t) * heads + h) * nsplit + blockIdx.z;
+    for (int d = lane; d < kv_rank; d += 32) part_o[pi * kv_rank + d] = os[warp * kv_rank + d];
+    if (lane == 0) {
+      part_ml[pi * 2] = m;
+      part_ml[pi * 2 + 1] = l;
+    }
+  }
+}
+
+// one block per (token, head): the parts of a split run and the sink meet in one softmax
+template <typename T>
+__global__ void latent_attn_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml, const float* __restrict__ sink, int heads,
+                                         int kv_rank, int nsplit) {
+  const size_t th = blockIdx.x;
+  const int h = static_cast<int>(th % heads);
+  const float* ml = part_ml + th * nsplit * 2;
+  float m = sink ? sink[h] : -1e30f;
+  for (int z = 0; z < nsplit; ++z) m = fmaxf(m, ml[2 * z]);
+  float l = sink ? expf(sink[h] - m) : 0.f;
+  for (int z = 0; z < nsplit; ++z) l += ml[2 * z + 1] * expf(ml[2 * z] - m);
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < nsplit; ++z) acc += part_o[(th * nsplit + z) * kv_rank + d] * expf(ml[2 * z] - m);
+    st(out + th * kv_rank + d, acc * inv);
   }
 }
 
@@ -178,9 +213,22 @@ void launch_latent_prep(const float* qc, int ldq, void* q_plain, float* q_full, 
   B200_CUDA_LAUNCH_CHECK();
 }
 
+int latent_attn_splits(int T, int heads, int window) {
+  const int nw = heads >= 8 ? 8 : (heads >= 4 ? 4 : (heads >= 2 ? 2 : 1));
+  const int blocks = T * ((heads + nw - 1) / nw);
+  int n = (2 * sm_count() + blocks - 1) / blocks;           // aim at two blocks per SM
+  if (window > 0) n = std::min(n, (window + 31) / 32);
+  return std::max(1, std::min(n, 16));
+}
+size_t latent_attn_workspace_bytes(int T, int heads, int kv_rank, int window) {
+  const int n = latent_attn_splits(T, heads, window);
+  return n == 1 ? 0 : static_cast<size_t>(T) * heads * n * (kv_rank + 2) * 4;
+}
+
 void launch_latent_attn(void* out, const float* q_full, const void* cache, const float* sink, const uint32_t* cu,
                         const uint32_t* ctx, const uint32_t* block_tables, int max_blocks, int num_seqs, int T,
-                        int heads, int kv_rank, int rot_dim, int window, float scale, int dt, cudaStream_t st_) {
+                        int heads, int kv_rank, int rot_dim, int window, float scale, int dt, void* workspace,
+                        cudaStream_t st_) {
   if (T <= 0) return;
   const int R = kv_rank + rot_dim, Rp = R | 1;
   const int nw = heads >= 8 ? 8 : (heads >= 4 ? 4 : (heads >= 2 ? 2 : 1));
@@ -192,20 +240,35 @@ void launch_latent_attn(void* out, const float* q_full, const void* cache, const
     set_error(1, "latent_attn: kv_rank + rot_dim too large for the shared-memory tile");
     return;
   }
-  const dim3 grid(T, (heads + nw - 1) / nw);
+  // few token rows (decoding): the keys of a row are split over several blocks and merged afterwards
+  const int nsplit = workspace ? latent_attn_splits(T, heads, window) : 1;
+  float* part_o = reinterpret_cast<float*>(workspace);
+  float* part_ml = part_o ? part_o + static_cast<size_t>(T) * heads * nsplit * kv_rank : nullptr;
+  const dim3 grid(T, (heads + nw - 1) / nw, nsplit);
   if (dt) {
     auto kern = latent_attn_kernel<float>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, nw * 32, smem, st_>>>((float*)out, q_full, (const float*)cache, sink, cu, ctx, block_tables,
-                                       max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale, key_tile);
+                                       max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale, key_tile, nsplit,
+                                       part_o, part_ml);
   } else {
     auto kern = latent_attn_kernel<__nv_bfloat16>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     kern<<<grid, nw * 32, smem, st_>>>((__nv_bfloat16*)out, q_full, (const __nv_bfloat16*)cache, sink, cu, ctx,
                                        block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale,
-                                       key_tile);
+                                       key_tile, nsplit, part_o, part_ml);
   }
   B200_CUDA_LAUNCH_CHECK();
+  if (nsplit > 1) {
+    const int th = kv_rank >= 256 ? 256 : 128;
+    if (dt)
+      latent_attn_merge_kernel<float><<<T * heads, th, 0, st_>>>((float*)out, part_o, part_ml, sink, heads, kv_rank,
+                                                                 nsplit);
+    else
+      latent_attn_merge_kernel<__nv_bfloat16><<<T * heads, th, 0, st_>>>((__nv_bfloat16*)out, part_o, part_ml, sink,
+                                                                         heads, kv_rank, nsplit);
+    B200_CUDA_LAUNCH_CHECK();
+  }
 }
 
 }  // namespace b200
@@ -226,12 +289,15 @@ void b200_latent_prep(const float* qc, int32_t ldq, void* q_plain, float* q_full
 void b200_latent_attn(void* out, const float* q_full, const void* cache, const float* sink,
                       const uint32_t* cu_seqlens_q, const uint32_t* context_lens, const uint32_t* block_tables,
                       int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens, int32_t heads, int32_t kv_rank,
-                      int32_t rot_dim, int32_t window, float scale, int32_t dt, int64_t stream) {
+                      int32_t rot_dim, int32_t window, float scale, int32_t dt, void* workspace, int64_t stream) {
   B200_CHECK_ARG(out && q_full && cache && cu_seqlens_q && context_lens && block_tables && num_seqs > 0 && heads > 0 &&
                      kv_rank > 0 && rot_dim >= 0 && (dt == 0 || dt == 1),
                  "latent_attn: bad arguments");
   b200::launch_latent_attn(out, q_full, cache, sink, cu_seqlens_q, context_lens, block_tables, max_blocks_per_seq,
-                           num_seqs, num_tokens, heads, kv_rank, rot_dim, window, scale, dt,
+                           num_seqs, num_tokens, heads, kv_rank, rot_dim, window, scale, dt, workspace,
                            reinterpret_cast<cudaStream_t>(stream));
+}
+int64_t b200_latent_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_rank, int32_t window) {
+  return static_cast<int64_t>(b200::latent_attn_workspace_bytes(num_tokens, heads, kv_rank, window));
 }
 }

@@ -81,7 +81,8 @@ void launch_latent_prep(const float* qc, int ldq, void* q_plain, float* q_full, 
                         int heads, int dim, int rot_dim, int rot_dims, int kv_rank, float eps, int dt, cudaStream_t st);
 void launch_latent_attn(void* out, const float* q_full, const void* cache, const float* sink, const uint32_t* cu,
                         const uint32_t* ctx, const uint32_t* block_tables, int max_blocks, int num_seqs, int T, int heads,
-                        int kv_rank, int rot_dim, int window, float scale, int dt, cudaStream_t st);
+                        int kv_rank, int rot_dim, int window, float scale, int dt, void* workspace, cudaStream_t st);
+size_t latent_attn_workspace_bytes(int T, int heads, int kv_rank, int window);
 
 void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const float* taps_w, const float* bias,
                             float* state, const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs,

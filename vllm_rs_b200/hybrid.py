@@ -96,6 +96,10 @@ class HybridRunner:
         self.out_rows = pin(T, torch.int32).view(np.uint32)
         self.out_ids = pin(T, torch.int32).view(np.uint32)
         self.out_logits = None          # pinned [rows, vocab], grown on demand
+        # steps run on a stream of their own (small steps are replayed as CUDA graphs, which the legacy default
+        # stream cannot capture); everything above was issued on the current stream
+        self.stream = torch.cuda.Stream(device=self.device)
+        torch.cuda.synchronize(self.device)
 
     def __del__(self):
         if getattr(self, "_h", None):
@@ -109,7 +113,7 @@ class HybridRunner:
         assert rc == 0
 
     def set_step_seed(self, seed, stream=None):
-        st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
+        st = stream if stream is not None else self.stream.cuda_stream
         self._l.b200_hybrid_set_step_seed(self._h, int(seed) & ((1 << 64) - 1), st)
         _lib.check()
 
@@ -125,12 +129,13 @@ class HybridRunner:
             if self.out_logits is None or self.out_logits.size < need:
                 self.out_logits = torch.zeros(need, dtype=torch.float32).pin_memory().numpy()
             lg = self.out_logits[:need].reshape(R, self.cfg.vocab)
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))     # e.g. caches filled by the caller
         rc = self._l.b200_hybrid_step_host(
             self._h, meta["input_ids"].ctypes.data, meta["positions"].ctypes.data, meta["slot_mapping"].ctypes.data,
             meta["cu_seqlens_q"].ctypes.data, meta["context_lens"].ctypes.data, meta["block_tables"].ctypes.data,
             meta["state_slots"].ctypes.data, self.out_rows.ctypes.data, B, T, meta["max_blocks"], R,
             0 if lg is None else lg.ctypes.data, self.out_ids.ctypes.data if (want_ids and R) else 0,
-            torch.cuda.current_stream().cuda_stream)
+            self.stream.cuda_stream)
         _lib.check()
         if rc != 0:
             raise _lib.B200Error("hybrid step failed")

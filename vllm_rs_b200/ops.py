@@ -353,14 +353,18 @@ def latent_prep(qc, cache, latent_norm_w, rot_freq, rot_mag, positions, slot_map
     return q_plain, q_full
 
 
-def latent_attn(q_full, cache, sink, cu_seqlens_q, context_lens, block_tables, *, kv_rank, rot_dim, window, scale):
-    """Attention-weighted latents [T, heads, kv_rank] in the cache dtype."""
+def latent_attn(q_full, cache, sink, cu_seqlens_q, context_lens, block_tables, *, kv_rank, rot_dim, window, scale,
+                split=True):
+    """Attention-weighted latents [T, heads, kv_rank] in the cache dtype.  split: give the kernel the workspace that
+    lets steps of few rows spread a row's keys over several blocks."""
     _cuda(q_full, cache, sink, cu_seqlens_q, context_lens, block_tables)
     T, H, _ = q_full.shape
     out = torch.empty(T, H, kv_rank, dtype=cache.dtype, device=q_full.device)
+    nbytes = _lib.lib().b200_latent_attn_workspace_bytes(T, H, kv_rank, int(window)) if split else 0
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q_full.device) if nbytes else None
     _lib.lib().b200_latent_attn(_p(out), _p(q_full), _p(cache), _p(sink), _p(cu_seqlens_q), _p(context_lens),
                                 _p(block_tables), block_tables.shape[1], context_lens.shape[0], T, H, kv_rank, rot_dim,
-                                int(window), float(scale), _dt(cache.dtype), _stream())
+                                int(window), float(scale), _dt(cache.dtype), _p(ws), _stream())
     _lib.check()
     return out
 
