@@ -697,11 +697,11 @@ void b200_latent_attn(void* out, const float* q_full, const void* cache, const f
                       int32_t rot_dim, int32_t window, float scale, int32_t dt, void* workspace, int64_t stream);
 int64_t b200_latent_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_rank, int32_t window);
 /* Causal per-channel convolution + SiLU; state fp32 [slots, taps - 1, channels]; taps_w fp32 [channels, taps] (last
- * column = current token), bias fp32 [channels] or NULL.  out may alias x.                                        */
+ * column = current token), bias fp32 [channels] or NULL.  out must not alias x (token chunks run in parallel).    */
 void b200_short_conv_silu(float* out, int32_t ldo, const float* x, int32_t ldx, const float* taps_w, const float* bias,
                           float* state, const int32_t* state_slots, const uint32_t* cu_seqlens_q,
-                          const uint32_t* context_lens, int32_t num_seqs, int32_t channels, int32_t taps,
-                          int64_t stream);
+                          const uint32_t* context_lens, int32_t num_seqs, int32_t num_tokens, int32_t channels,
+                          int32_t taps, int64_t stream);
 /* q, k [T, kv_heads, dim], v [T, heads, vdim] (row stride ld), b_raw / a_raw [T, heads] (row stride ld_ba), all fp32;
  * out fp32 [T, heads, vdim]; state fp32 [slots, heads, dim, vdim].                                                 */
 void b200_delta_rule(float* out, const float* q, const float* k, const float* v, int32_t ld, const float* b_raw,

@@ -238,7 +238,7 @@ _SIGS = {
     "b200_latent_prep": (None, [c_vp, c_i32] + [c_vp] * 5 + [c_f32, c_vp, c_vp] + [c_i32] * 6 + [c_f32, c_i32, c_i64]),
     "b200_latent_attn": (None, [c_vp] * 7 + [c_i32] * 7 + [c_f32, c_i32, c_vp, c_i64]),
     "b200_latent_attn_workspace_bytes": (c_i64, [c_i32] * 4),
-    "b200_short_conv_silu": (None, [c_vp, c_i32, c_vp, c_i32] + [c_vp] * 6 + [c_i32] * 3 + [c_i64]),
+    "b200_short_conv_silu": (None, [c_vp, c_i32, c_vp, c_i32] + [c_vp] * 6 + [c_i32] * 4 + [c_i64]),
     "b200_delta_rule": (None, [c_vp] * 4 + [c_i32, c_vp, c_vp, c_i32] + [c_vp] * 6 + [c_i32] * 5 + [c_i64]),
     "b200_ssd_scan": (None, [c_vp] * 4 + [c_i32, c_vp, c_i32] + [c_vp] * 7 + [c_i32] * 5 + [c_i64]),
     "b200_moe_route": (None, [c_vp, c_i32, c_i32, c_i32, c_f32, c_vp, c_vp, c_i64]),

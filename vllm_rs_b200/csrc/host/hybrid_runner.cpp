@@ -49,6 +49,7 @@ struct b200_hybrid {
   float* x = nullptr;          // [T, width] residual stream
   void* h = nullptr;           // [T, width] normed stream, operand dtype
   float* proj = nullptr;       // [T, max fused input projection]
+  float* conv = nullptr;       // [T, max convolved channels]: output of the short convolution
   float* aux = nullptr;        // [T, max(heads (kv_rank + rot_dim), heads vdim)] fp32: q_full / scan output / expanded values
   void* opa = nullptr;         // [T, max(heads dim, heads vdim, 2 shared... )] operand dtype: q_plain, then the o-projection input
   void* lat = nullptr;         // [T, heads kv_rank] operand dtype: attention-weighted latents
@@ -108,7 +109,7 @@ static int in_rows(const b200_hybrid_layer& l) {
 static int64_t carve(b200_hybrid* r, uint8_t* base) {
   const b200_hybrid_config& c = r->cfg;
   const size_t T = c.max_tokens, es = c.dt ? 4 : 2;
-  size_t proj_n = 1, aux_n = 1, opa_n = 1, lat_n = 1, E = 1, top = 1, sh_n = 1, moe_bytes = 256, attn_bytes = 0;
+  size_t conv_n = 1, proj_n = 1, aux_n = 1, opa_n = 1, lat_n = 1, E = 1, top = 1, sh_n = 1, moe_bytes = 256, attn_bytes = 0;
   // rows up to which a step may split its attention rows: beyond two blocks per SM a split is never chosen
   r->attn_ws_rows = std::min<size_t>(T, 2 * static_cast<size_t>(sm_count()));
   for (const b200_hybrid_layer& l : r->layers) {
@@ -122,6 +123,9 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
     } else {
       aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * l.vdim);
       opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * l.vdim);
+      conv_n = std::max<size_t>(conv_n, l.mixer == B200_MIXER_DELTA_RULE
+                                            ? 2 * static_cast<size_t>(l.kv_heads) * l.dim + static_cast<size_t>(l.heads) * l.vdim
+                                            : static_cast<size_t>(l.heads) * l.vdim + 2 * static_cast<size_t>(l.kv_heads) * l.state);
     }
     if (l.experts > 0) {
       E = std::max<size_t>(E, l.experts);
@@ -139,6 +143,7 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
   r->x = (float*)take(T * c.width * 4);
   r->h = take(T * c.width * es);
   r->proj = (float*)take(T * proj_n * 4);
+  r->conv = (float*)take(T * conv_n * 4);
   r->aux = (float*)take(T * aux_n * 4);
   r->opa = take(T * opa_n * es);
   r->lat = take(T * lat_n * es);
@@ -300,15 +305,15 @@ static void mixer_delta(b200_hybrid* r, const b200_hybrid_layer& l, const uint32
   const int H = l.heads, Hk = l.kv_heads, n_in = in_rows(l);
   const int nq = Hk * l.dim, nv = H * l.vdim, nconv = 2 * nq + nv;
   gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
-  launch_short_conv_silu(r->proj, n_in, r->proj, n_in, (const float*)l.conv_w, (const float*)l.conv_b,
-                         (float*)l.conv_state, state_slots, cu, ctx, B, nconv, l.conv_taps, st);
-  const float* q = r->proj;
-  const float* k = r->proj + nq;
-  const float* v = r->proj + 2 * nq;
+  launch_short_conv_silu(r->conv, nconv, r->proj, n_in, (const float*)l.conv_w, (const float*)l.conv_b,
+                         (float*)l.conv_state, state_slots, cu, ctx, B, T, nconv, l.conv_taps, st);
+  const float* q = r->conv;
+  const float* k = r->conv + nq;
+  const float* v = r->conv + 2 * nq;
   const float* b_raw = r->proj + nconv;
   const float* a_raw = b_raw + H;
   const float* gate = a_raw + H;
-  launch_delta_rule(r->aux, q, k, v, n_in, b_raw, a_raw, n_in, (const float*)l.a_log, (const float*)l.dt_bias,
+  launch_delta_rule(r->aux, q, k, v, nconv, b_raw, a_raw, n_in, (const float*)l.a_log, (const float*)l.dt_bias,
                     (float*)l.rec_state, state_slots, cu, ctx, B, H, Hk, l.dim, l.vdim, st);
   launch_gated_group_norm(r->opa, r->aux, nv, gate, n_in, (const float*)l.out_norm_w, l.vdim, T, nv, l.vdim, c.norm_eps,
                           0, c.dt, st);
@@ -321,10 +326,10 @@ static void mixer_ssd(b200_hybrid* r, const b200_hybrid_layer& l, const uint32_t
   const int H = l.heads, G = l.kv_heads, N = l.state, inner = H * l.vdim, n_in = in_rows(l);
   const int nconv = inner + 2 * G * N;
   gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
-  float* xbc = r->proj + inner;
-  launch_short_conv_silu(xbc, n_in, xbc, n_in, (const float*)l.conv_w, (const float*)l.conv_b, (float*)l.conv_state,
-                         state_slots, cu, ctx, B, nconv, l.conv_taps, st);
-  launch_ssd_scan(r->aux, xbc, xbc + inner, xbc + inner + G * N, n_in, xbc + nconv, n_in, (const float*)l.a_log,
+  const float* xbc = r->conv;
+  launch_short_conv_silu(r->conv, nconv, r->proj + inner, n_in, (const float*)l.conv_w, (const float*)l.conv_b,
+                         (float*)l.conv_state, state_slots, cu, ctx, B, T, nconv, l.conv_taps, st);
+  launch_ssd_scan(r->aux, xbc, xbc + inner, xbc + inner + G * N, nconv, r->proj + inner + nconv, n_in, (const float*)l.a_log,
                   (const float*)l.dt_bias, (const float*)l.d_skip, (float*)l.rec_state, state_slots, cu, ctx, B, H, G, N,
                   l.vdim, st);
   launch_gated_group_norm(r->opa, r->aux, inner, r->proj, n_in, (const float*)l.out_norm_w, inner, T, inner,

@@ -5,14 +5,16 @@
 // slot held before, so slots can be handed on without clearing.  Everything here is fp32.
 //
 //   short_conv_silu : y[t, c] = silu(bias[c] + sum_j w[c, j] * x[t - (taps-1) + j, c]); the last taps-1 inputs of a
-//                     sequence are its conv state  [slots, taps-1, C].
+//                     sequence are its conv state  [slots, taps-1, C].  Token chunks run in parallel; a second small
+//                     launch rolls the state forward.
 //   delta_rule      : per head, S [dim, vdim]:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //                     with q, k unit-normalised per head (q also times dim^-1/2), beta = sigmoid(b),
 //                     g = exp(-exp(a_log) * softplus(a + dt_bias)).  state [slots, heads, dim, vdim].
 //   ssd_scan        : per head, S [nstate, vdim]:  dt = softplus(dt_raw + dt_bias);  S <- exp(-exp(a_log) dt) S + dt B x^T;
 //                     y = S^T C + D x.  state [slots, heads, nstate, vdim].
-// In both scans a thread owns one column of S (one value channel) in registers and walks the sequence's tokens in
-// order: the exact recurrence, no chunked reformulation, so a portion boundary cannot change the arithmetic.
+// In both scans four lanes share one column of S (one value channel), each holding every fourth row in registers,
+// and walk the sequence's tokens in order: the exact recurrence, no chunked reformulation, so a portion boundary
+// cannot change the arithmetic.
 #include "../../include/b200_vllm.h"
 #include "seqmix.cuh"
 
@@ -21,25 +23,35 @@ using namespace seqmix;
 
 constexpr int kMaxTaps = 8;
 
+constexpr int kConvChunk = 64;      // tokens per thread
+
+// grid = (channel blocks, sequences, token chunks): every thread convolves one channel over one chunk of a sequence's
+// rows; the taps-1 inputs before the chunk come from the rows before it or, at the start of the step, from the
+// sequence's state (zeros when the sequence starts here).  out must not alias x.
 template <int TAPS>
 __global__ void short_conv_silu_kernel(float* __restrict__ out, int ldo, const float* __restrict__ x, int ldx,
                                        const float* __restrict__ taps_w, const float* __restrict__ bias,
-                                       float* __restrict__ state, const int32_t* __restrict__ slots,
+                                       const float* __restrict__ state, const int32_t* __restrict__ slots,
                                        const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx, int C) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
   if (c >= C) return;
   const int t0 = cu[b], t1 = cu[b + 1];
-  if (t1 <= t0) return;
+  const int start = t0 + static_cast<int>(blockIdx.z) * kConvChunk;
+  if (start >= t1) return;
+  const int end = min(t1, start + kConvChunk);
   const bool fresh = static_cast<int>(ctx[b]) == t1 - t0;
   constexpr int P = TAPS - 1;                  // inputs remembered between tokens
   float w[TAPS], win[P > 0 ? P : 1];
 #pragma unroll
   for (int j = 0; j < TAPS; ++j) w[j] = taps_w[static_cast<size_t>(c) * TAPS + j];
-  float* sp = state + static_cast<size_t>(slots[b]) * P * C + c;
+  const float* sp = state + static_cast<size_t>(slots[b]) * P * C + c;
 #pragma unroll
-  for (int j = 0; j < P; ++j) win[j] = fresh ? 0.f : sp[static_cast<size_t>(j) * C];     // oldest first
+  for (int j = 0; j < P; ++j) {                // oldest first
+    const int idx = start - P + j;
+    win[j] = idx >= t0 ? x[static_cast<size_t>(idx) * ldx + c] : (fresh ? 0.f : sp[static_cast<size_t>(P + idx - t0) * C]);
+  }
   const float bv = bias ? bias[c] : 0.f;
-  for (int t = t0; t < t1; ++t) {
+  for (int t = start; t < end; ++t) {
     const float xv = x[static_cast<size_t>(t) * ldx + c];
     float acc = bv;
 #pragma unroll
@@ -50,13 +62,35 @@ __global__ void short_conv_silu_kernel(float* __restrict__ out, int ldo, const f
     for (int j = 0; j + 1 < P; ++j) win[j] = win[j + 1];
     if (P > 0) win[P > 0 ? P - 1 : 0] = xv;
   }
+}
+
+// the sequence's last taps-1 inputs become its state (older ones slide over from the previous state)
+template <int TAPS>
+__global__ void short_conv_state_kernel(const float* __restrict__ x, int ldx, float* __restrict__ state,
+                                        const int32_t* __restrict__ slots, const uint32_t* __restrict__ cu,
+                                        const uint32_t* __restrict__ ctx, int C) {
+  constexpr int P = TAPS - 1;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (c >= C || P == 0) return;
+  const int t0 = cu[b], t1 = cu[b + 1];
+  if (t1 <= t0) return;
+  const bool fresh = static_cast<int>(ctx[b]) == t1 - t0;
+  float* sp = state + static_cast<size_t>(slots[b]) * P * C + c;
+  float keep[P > 0 ? P : 1];
 #pragma unroll
-  for (int j = 0; j < P; ++j) sp[static_cast<size_t>(j) * C] = win[j];
+  for (int j = 0; j < P; ++j) {
+    const int idx = t1 - P + j;
+    keep[j] = idx >= t0 ? x[static_cast<size_t>(idx) * ldx + c] : (fresh ? 0.f : sp[static_cast<size_t>(P + idx - t0) * C]);
+  }
+#pragma unroll
+  for (int j = 0; j < P; ++j) sp[static_cast<size_t>(j) * C] = keep[j];
 }
 
 constexpr int kChunk = 8;          // tokens staged in shared memory per pass
+constexpr int kRowSplit = 4;       // lanes that share one column of S (each holds every 4th row)
 
-// grid = (column blocks, heads, sequences); DK = compile-time bound of `dim` (rows of S held per thread)
+// grid = (column blocks, heads, sequences); block = 128 threads = 32 columns x kRowSplit lanes.  DK = compile-time
+// bound of `dim`; a lane holds the rows i = j * kRowSplit + part of its column.
 template <int DK>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k,
@@ -65,18 +99,23 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
                   const float* __restrict__ dt_bias, float* __restrict__ state, const int32_t* __restrict__ slots,
                   const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx, int heads, int kv_heads, int dim,
                   int vdim) {
+  constexpr int RS = kRowSplit, NR = DK / RS;
   __shared__ float ks[kChunk][DK], qs[kChunk][DK], gs[kChunk], bs[kChunk];
   const int h = blockIdx.y, b = blockIdx.z;
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const int part = threadIdx.x % RS;
+  const int col = blockIdx.x * (blockDim.x / RS) + threadIdx.x / RS;
   const bool live = col < vdim;
   const int t0 = cu[b], t1 = cu[b + 1];
   if (t1 <= t0) return;
   const bool fresh = static_cast<int>(ctx[b]) == t1 - t0;
   const int hk = h / (heads / kv_heads);
   float* sp = state + ((static_cast<size_t>(slots[b]) * heads + h) * dim) * vdim + col;
-  float s[DK];
+  float s[NR];
 #pragma unroll
-  for (int i = 0; i < DK; ++i) s[i] = (!fresh && live && i < dim) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
+  for (int j = 0; j < NR; ++j) {
+    const int i = j * RS + part;
+    s[j] = (!fresh && live && i < dim) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
+  }
   const float neg_a = -expf(a_log[h]), dtb = dt_bias[h], qscale = rsqrtf(static_cast<float>(dim));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   for (int c0 = t0; c0 < t1; c0 += kChunk) {
@@ -104,29 +143,45 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
       }
     }
     __syncthreads();
-    if (!live) continue;
-    for (int r = 0; r < n; ++r) {
+    for (int r = 0; r < n; ++r) {          // every lane runs the shuffles; dead columns carry zeros
       const float g = gs[r];
-      float dot = 0.f;
+      float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < DK; ++i) {
-        s[i] *= g;
-        dot += ks[r][i] * s[i];
+      for (int j = 0; j < NR; j += 2) {
+        s[j] *= g;
+        d0 += ks[r][j * RS + part] * s[j];
+        if (j + 1 < NR) {
+          s[j + 1] *= g;
+          d1 += ks[r][(j + 1) * RS + part] * s[j + 1];
+        }
       }
-      const float u = bs[r] * (v[static_cast<size_t>(c0 + r) * ld + h * vdim + col] - dot);
-      float o = 0.f;
+      float dot = d0 + d1;
 #pragma unroll
-      for (int i = 0; i < DK; ++i) {
-        s[i] += ks[r][i] * u;
-        o += qs[r][i] * s[i];
+      for (int o = 1; o < RS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float vv = live ? v[static_cast<size_t>(c0 + r) * ld + h * vdim + col] : 0.f;
+      const float u = bs[r] * (vv - dot);
+      float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NR; j += 2) {
+        s[j] += ks[r][j * RS + part] * u;
+        o0 += qs[r][j * RS + part] * s[j];
+        if (j + 1 < NR) {
+          s[j + 1] += ks[r][(j + 1) * RS + part] * u;
+          o1 += qs[r][(j + 1) * RS + part] * s[j + 1];
+        }
       }
-      out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = o;
+      float o = o0 + o1;
+#pragma unroll
+      for (int x = 1; x < RS; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+      if (live && part == 0) out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = o;
     }
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i)
-      if (i < dim) sp[static_cast<size_t>(i) * vdim] = s[i];
+    for (int j = 0; j < NR; ++j) {
+      const int i = j * RS + part;
+      if (i < dim) sp[static_cast<size_t>(i) * vdim] = s[j];
+    }
   }
 }
 
@@ -137,18 +192,23 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
                 const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ d_skip,
                 float* __restrict__ state, const int32_t* __restrict__ slots, const uint32_t* __restrict__ cu,
                 const uint32_t* __restrict__ ctx, int heads, int groups, int nstate, int vdim) {
+  constexpr int RS = kRowSplit, NR = NS / RS;
   __shared__ float Bs[kChunk][NS], Cs[kChunk][NS], dts[kChunk], das[kChunk];
   const int h = blockIdx.y, b = blockIdx.z;
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  const int part = threadIdx.x % RS;
+  const int col = blockIdx.x * (blockDim.x / RS) + threadIdx.x / RS;
   const bool live = col < vdim;
   const int t0 = cu[b], t1 = cu[b + 1];
   if (t1 <= t0) return;
   const bool fresh = static_cast<int>(ctx[b]) == t1 - t0;
   const int g = h / (heads / groups);
   float* sp = state + ((static_cast<size_t>(slots[b]) * heads + h) * nstate) * vdim + col;
-  float s[NS];
+  float s[NR];
 #pragma unroll
-  for (int i = 0; i < NS; ++i) s[i] = (!fresh && live && i < nstate) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
+  for (int j = 0; j < NR; ++j) {
+    const int i = j * RS + part;
+    s[j] = (!fresh && live && i < nstate) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
+  }
   const float neg_a = -expf(a_log[h]), dtb = dt_bias[h], dsk = d_skip ? d_skip[h] : 0.f;
   for (int c0 = t0; c0 < t1; c0 += kChunk) {
     const int n = min(kChunk, t1 - c0);
@@ -164,38 +224,52 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
       das[threadIdx.x] = expf(neg_a * dt);
     }
     __syncthreads();
-    if (!live) continue;
     for (int r = 0; r < n; ++r) {
-      const float xv = x[static_cast<size_t>(c0 + r) * ld + h * vdim + col];
+      const float xv = live ? x[static_cast<size_t>(c0 + r) * ld + h * vdim + col] : 0.f;
       const float a = das[r], dx = dts[r] * xv;
-      float y = 0.f;
+      float y0 = 0.f, y1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < NS; ++i) {
-        s[i] = a * s[i] + dx * Bs[r][i];
-        y += Cs[r][i] * s[i];
+      for (int j = 0; j < NR; j += 2) {
+        s[j] = a * s[j] + dx * Bs[r][j * RS + part];
+        y0 += Cs[r][j * RS + part] * s[j];
+        if (j + 1 < NR) {
+          s[j + 1] = a * s[j + 1] + dx * Bs[r][(j + 1) * RS + part];
+          y1 += Cs[r][(j + 1) * RS + part] * s[j + 1];
+        }
       }
-      out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = y + dsk * xv;
+      float y = y0 + y1;
+#pragma unroll
+      for (int o = 1; o < RS; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (live && part == 0) out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = y + dsk * xv;
     }
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < NS; ++i)
-      if (i < nstate) sp[static_cast<size_t>(i) * vdim] = s[i];
+    for (int j = 0; j < NR; ++j) {
+      const int i = j * RS + part;
+      if (i < nstate) sp[static_cast<size_t>(i) * vdim] = s[j];
+    }
   }
 }
 
 void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const float* taps_w, const float* bias,
                             float* state, const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs,
-                            int C, int taps, cudaStream_t st_) {
-  if (num_seqs <= 0 || C <= 0) return;
+                            int num_rows, int C, int taps, cudaStream_t st_) {
+  if (num_seqs <= 0 || C <= 0 || num_rows <= 0) return;
   if (taps < 1 || taps > kMaxTaps) {
     set_error(1, "short_conv: between 1 and 8 taps are supported");
     return;
   }
-  const dim3 grid((C + 127) / 128, num_seqs);
+  if (out == x) {
+    set_error(1, "short_conv: the output must not alias the input (chunks of a sequence run in parallel)");
+    return;
+  }
+  const dim3 grid((C + 127) / 128, num_seqs, (num_rows + kConvChunk - 1) / kConvChunk);
+  const dim3 sgrid((C + 127) / 128, num_seqs);
 #define B200_CONV(K)                                                                                              \
   case K:                                                                                                         \
     short_conv_silu_kernel<K><<<grid, 128, 0, st_>>>(out, ldo, x, ldx, taps_w, bias, state, slots, cu, ctx, C); \
+    if (K > 1) short_conv_state_kernel<K><<<sgrid, 128, 0, st_>>>(x, ldx, state, slots, cu, ctx, C);           \
     break
   switch (taps) {
     B200_CONV(1); B200_CONV(2); B200_CONV(3); B200_CONV(4); B200_CONV(5); B200_CONV(6); B200_CONV(7); B200_CONV(8);
@@ -204,15 +278,15 @@ void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const 
   B200_CUDA_LAUNCH_CHECK();
 }
 
-static int col_threads(int vdim) { return vdim >= 128 ? 128 : (vdim > 32 ? 64 : 32); }
+constexpr int kScanThreads = 128, kScanCols = kScanThreads / kRowSplit;      // columns of S per block
 
 void launch_delta_rule(float* out, const float* q, const float* k, const float* v, int ld, const float* b_raw,
                        const float* a_raw, int ld_ba, const float* a_log, const float* dt_bias, float* state,
                        const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads,
                        int kv_heads, int dim, int vdim, cudaStream_t st_) {
   if (num_seqs <= 0) return;
-  const int th = col_threads(vdim);
-  const dim3 grid((vdim + th - 1) / th, heads, num_seqs);
+  const int th = kScanThreads;
+  const dim3 grid((vdim + kScanCols - 1) / kScanCols, heads, num_seqs);
 #define B200_DELTA(DK)                                                                                              \
   delta_rule_kernel<DK><<<grid, th, 0, st_>>>(out, q, k, v, ld, b_raw, a_raw, ld_ba, a_log, dt_bias, state, slots, \
                                               cu, ctx, heads, kv_heads, dim, vdim)
@@ -234,8 +308,8 @@ void launch_ssd_scan(float* out, const float* x, const float* Bm, const float* C
                      const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads, int groups,
                      int nstate, int vdim, cudaStream_t st_) {
   if (num_seqs <= 0) return;
-  const int th = col_threads(vdim);
-  const dim3 grid((vdim + th - 1) / th, heads, num_seqs);
+  const int th = kScanThreads;
+  const dim3 grid((vdim + kScanCols - 1) / kScanCols, heads, num_seqs);
 #define B200_SSD(NS)                                                                                               \
   ssd_scan_kernel<NS><<<grid, th, 0, st_>>>(out, x, Bm, Cm, ld, dt_raw, ld_dt, a_log, dt_bias, d_skip, state, slots, \
                                             cu, ctx, heads, groups, nstate, vdim)
@@ -257,11 +331,11 @@ void launch_ssd_scan(float* out, const float* x, const float* Bm, const float* C
 extern "C" {
 void b200_short_conv_silu(float* out, int32_t ldo, const float* x, int32_t ldx, const float* taps_w, const float* bias,
                           float* state, const int32_t* state_slots, const uint32_t* cu_seqlens_q,
-                          const uint32_t* context_lens, int32_t num_seqs, int32_t channels, int32_t taps,
-                          int64_t stream) {
+                          const uint32_t* context_lens, int32_t num_seqs, int32_t num_tokens, int32_t channels,
+                          int32_t taps, int64_t stream) {
   B200_CHECK_ARG(out && x && taps_w && state && state_slots && cu_seqlens_q && context_lens, "short_conv: bad arguments");
   b200::launch_short_conv_silu(out, ldo, x, ldx, taps_w, bias, state, state_slots, cu_seqlens_q, context_lens, num_seqs,
-                               channels, taps, reinterpret_cast<cudaStream_t>(stream));
+                               num_tokens, channels, taps, reinterpret_cast<cudaStream_t>(stream));
 }
 void b200_delta_rule(float* out, const float* q, const float* k, const float* v, int32_t ld, const float* b_raw,
                      const float* a_raw, int32_t ld_ba, const float* a_log, const float* dt_bias, float* state,

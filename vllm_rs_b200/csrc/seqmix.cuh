@@ -86,7 +86,7 @@ size_t latent_attn_workspace_bytes(int T, int heads, int kv_rank, int window);
 
 void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const float* taps_w, const float* bias,
                             float* state, const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs,
-                            int C, int taps, cudaStream_t st);
+                            int num_rows, int C, int taps, cudaStream_t st);
 void launch_delta_rule(float* out, const float* q, const float* k, const float* v, int ld, const float* b_raw,
                        const float* a_raw, int ld_ba, const float* a_log, const float* dt_bias, float* state,
                        const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads,

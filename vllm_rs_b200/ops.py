@@ -375,7 +375,7 @@ def short_conv_silu(x, taps_w, bias, state, state_slots, cu_seqlens_q, context_l
     out = torch.empty_like(x)
     _lib.lib().b200_short_conv_silu(_p(out), x.shape[1], _p(x), x.shape[1], _p(taps_w), _p(bias), _p(state),
                                     _p(state_slots), _p(cu_seqlens_q), _p(context_lens), context_lens.shape[0],
-                                    x.shape[1], taps_w.shape[1], _stream())
+                                    x.shape[0], x.shape[1], taps_w.shape[1], _stream())
     _lib.check()
     return out
 
