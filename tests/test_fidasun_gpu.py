@@ -28,6 +28,8 @@ def toks(n, vocab, seed):
     ("latent_attention", dict(heads=5, dim=8, rot_dim=12, vdim=8, kv_rank=24, mask=None,
                               rot={"base": 500.0, "dims": 12, "scaling": None})),
     ("latent_attention", dict(heads=9, mask={"size": 64}, rot={"base": 10000.0, "dims": 8, "scaling": None})),
+    ("latent_attention", dict(heads=3, dim=16, rot_dim=16, vdim=24, kv_rank=64, mask={"size": 37})),   # tensor-core form
+    ("latent_attention", dict(heads=2, dim=8, rot_dim=32, vdim=40, kv_rank=128, mask=None)),
     ("delta", {}),
     ("delta", dict(heads=2, kv_heads=2, dim=40, vdim=70, conv=4)),
     ("mamba2", {}),
@@ -177,12 +179,13 @@ def test_delta_rule_and_ssd_ops_in_portions(lib):
 @pytest.mark.parametrize("window", [0, 5, 64, 70, 130])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("split", [True, False])
-def test_latent_attention_sees_exactly_its_window(lib, window, dtype, split):
+@pytest.mark.parametrize("r,dr", [(12, 4), (64, 16)])        # the second shape takes the tensor-core form for many rows
+def test_latent_attention_sees_exactly_its_window(lib, window, dtype, split, r, dr):
     """Every cached latent is a distinct random vector and the query is made to score the EARLIEST visible key far
     above all others: the output must be the latent at the window's far edge, never the one just outside it; checked
     for prompt rows and for single decoded rows, with edges at page borders and far back, on a shuffled block table."""
     from vllm_rs_b200 import ops
-    r, dr, H, n = 12, 4, 2, 200
+    H, n = 2, 200
     R_ = r + dr
     pages = [5, 2, 7, 0]                                               # shuffled physical pages
     cache = torch.zeros(8, 64, R_, dtype=dtype, device="cuda")
@@ -198,7 +201,7 @@ def test_latent_attention_sees_exactly_its_window(lib, window, dtype, split):
     # the rotated query part is a steep NEGATIVE ramp over the position tag: the earliest visible key outweighs all
     # later ones by e^-20 per position, so the output is the latent at the window's far edge (or key 0 without a
     # window), and a key one place outside the window would have won had it been seen
-    for rows_pos in ([199], [64], [63], list(range(120, 200)), list(range(0, 70))):
+    for rows_pos in ([199], [64], [63], list(range(100, 200)), list(range(120, 200)), list(range(0, 70)), list(range(0, 129))):
         T = len(rows_pos)
         q = torch.zeros(T, H, R_)
         q[:, :, r:] = -4000.0 / dr                                     # prefers the earliest visible key

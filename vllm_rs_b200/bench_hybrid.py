@@ -87,6 +87,7 @@ def _say(msg):
 
 
 def _time(fn, reps, warm=3):
+    """ms per call on the current stream: warm-up, then CUDA events around `reps` calls."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -226,26 +227,53 @@ def run(size="w2048", layers=4, prefill=4096, batch=32, ctx=2048, reps=5):
     _say(f"fidasun: {res['fidasun']}")
     del r
     torch.cuda.empty_cache()
-    # ---- the dense fp16 LLaMA plan at equal width / depth / active feed-forward size
+    # ---- the dense fp16 LLaMA plan at equal width / depth / active feed-forward size, in a process of its own with a
+    # time limit (an arm that does not answer is reported as such instead of stalling the whole bench)
+    import subprocess
+    import sys
+    try:
+        out = subprocess.run([sys.executable, "-m", "vllm_rs_b200.bench_hybrid", size, str(layers), str(prefill),
+                              str(batch), str(ctx), str(reps)], capture_output=True, text=True, timeout=180,
+                             cwd=str(Path(__file__).resolve().parent.parent))
+        line = [x for x in out.stdout.splitlines() if x.startswith("{")]
+        res["llama_fp16"] = json.loads(line[-1]) if line else {"unavailable": f"exit {out.returncode}: {out.stderr[-300:]}"}
+    except subprocess.TimeoutExpired:
+        res["llama_fp16"] = {"unavailable": "no answer within 180 s"}
+    _say(f"llama fp16: {res['llama_fp16']}")
+    res["kernels"] = kernel_table(size, prefill, batch, ctx, peaks)
+    return res
+
+
+def dense_arm(size, layers, prefill, batch, ctx, reps):
+    """Prefill and decode of the dense fp16 LLaMA plan at the width / depth / active feed-forward size of `size`, on a
+    stream of its own as the other benches run it."""
+    s = SIZES[size]
+    nblk = (max(prefill, ctx) + 63) // 64
     H, Hkv, Dh, inter = s["dense"]
     name = f"dense-{size}"
     synthetic.SHAPES[name] = (s["width"], layers, H, Hkv, Dh, inter, s["vocab"], 10000.0)
     lr = synthetic.build_runner(name, "fp16", num_blocks=batch * nblk, max_blocks_per_seq=nblk, max_batch=batch,
                                 num_layers=layers, max_prefill_tokens=prefill)
     synthetic.fill_kv_random(lr)
+    mp, md = _meta(1, prefill, prefill, nblk, s["vocab"]), _meta(batch, 1, ctx, nblk, s["vocab"])
     meta = dict(input_ids=mp["input_ids"], positions=mp["positions"], slot_mapping=mp["slot_mapping"],
                 cu_seqlens_q=mp["cu_seqlens_q"], context_lens=None, block_tables=mp["block_tables"].reshape(1, nblk),
                 max_seqlen_q=prefill)
-    ms = _time(lambda: lr.prefill_device(meta, want_logits=False), reps, warm=2)
-    res["llama_fp16"] = {"prefill_ms": ms, "prefill_tok_s": prefill * 1e3 / ms}
-    dev = "cuda"
-    t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a).astype(dt)).to(dev)          # noqa: E731
-    ids, pos, slot = t(md["input_ids"], np.int32), t(md["positions"], np.int64), t(md["slot_mapping"], np.int64)
-    bt, cl = t(md["block_tables"].reshape(batch, nblk), np.int32), t(md["context_lens"], np.int32)
-    ms = _time(lambda: lr.decode_device(ids, pos, slot, bt, cl, want_logits=False), reps * 4, warm=3)
-    res["llama_fp16"].update(decode_ms=ms, decode_tok_s=batch * 1e3 / ms, launches=int(lr.launches_per_step))
-    _say(f"llama fp16: {res['llama_fp16']}")
-    del lr
-    torch.cuda.empty_cache()
-    res["kernels"] = kernel_table(size, prefill, batch, ctx, peaks)
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        ms = _time(lambda: lr.prefill_device(meta, want_logits=False), reps, warm=2)
+        res = {"prefill_ms": ms, "prefill_tok_s": prefill * 1e3 / ms}
+        t = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a).astype(dt)).to("cuda")          # noqa: E731
+        ids, pos, slot = t(md["input_ids"], np.int32), t(md["positions"], np.int64), t(md["slot_mapping"], np.int64)
+        bt, cl = t(md["block_tables"].reshape(batch, nblk), np.int32), t(md["context_lens"], np.int32)
+        ms = _time(lambda: lr.decode_device(ids, pos, slot, bt, cl, want_logits=False), reps * 4, warm=3)
+        res.update(decode_ms=ms, decode_tok_s=batch * 1e3 / ms, launches=int(lr.launches_per_step))
     return res
+
+
+if __name__ == "__main__":
+    import json as _json
+    import sys as _sys
+    a = _sys.argv[1:]
+    print(_json.dumps(dense_arm(a[0], int(a[1]), int(a[2]), int(a[3]), int(a[4]), int(a[5]))), flush=True)

@@ -10,7 +10,10 @@
 // W_uv[h].  All heads of a token read the same cache rows (multi-query form), which is what makes the latent cache
 // cheap to stream.  Options: sliding window (position i sees j with 0 <= i - j < window; window <= 0 = all), and a
 // learned per-head sink logit that joins the softmax denominator without a key or value.
-// Beside paged_attn_decode.cu / attn_prefill*.cu (per-head K / V caches, fp16 / bf16, no window over prompts).
+// Two kernels: an fp32 FMA form (any sizes, both dtypes; rows of small steps split their keys over several blocks and
+// merge) and a bf16 tensor-core form for steps of many rows (kv_rank a multiple of 64 up to 512, kv_rank + rot_dim a
+// multiple of 16).  Beside paged_attn_decode.cu / attn_prefill*.cu (per-head K / V caches, fp16 / bf16, no window
+// over prompts).
 //
 // latent_prep_kernel: from the fused projection row [q (H x (dim + rot_dim)) | c_raw (kv_rank) | k_rot_raw (rot_dim)]
 // (fp32) it RMS-norms the latent (plain weight), rotates the first rot_dims entries of every head's rotated query
@@ -18,6 +21,7 @@
 // cos / sin scaled by rot_mag), writes the cache row at the token's slot, and splits the queries.
 #include "../../include/b200_vllm.h"
 #include <algorithm>
+#include <cstdlib>
 
 #include "seqmix.cuh"
 
@@ -213,6 +217,226 @@ void launch_latent_prep(const float* qc, int ldq, void* q_plain, float* q_full, 
   B200_CUDA_LAUNCH_CHECK();
 }
 
+// ---- bf16 tensor-core form for steps of many rows (prompt portions).  Block = 4 warps = one head x 16 consecutive
+// token rows of ONE sequence.  Per tile of 64 keys: every warp computes the scores of 16 keys (S = Q K^T, mma.sync
+// m16n8k16 bf16 -> fp32, Q and K from shared memory), the fp32 scores meet in shared memory, every warp runs the same
+// fp32 online softmax over all 64 (sink as the initial denominator, window and causal mask per element) and
+// multiplies P (bf16) with ITS quarter of the latent columns (V fragments by ldmatrix.trans from the same key tile).
+constexpr int MQ = 16, MKT = 64;
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// NT = n-tiles (8 latent columns each) per warp = kv_rank / 32
+template <int NT>
+__global__ void __launch_bounds__(128)
+latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ q_full,
+                       const __nv_bfloat16* __restrict__ cache, const float* __restrict__ sink,
+                       const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
+                       const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_rank,
+                       int rot_dim, int window, float scale) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int R = kv_rank + rot_dim, P = R + 8;             // P: row pitch in bf16 elements (16-byte multiple)
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [MKT][P]
+  __nv_bfloat16* Qs = Ks + static_cast<size_t>(MKT) * P;                    // [MQ][P]
+  float* Ss = reinterpret_cast<float*>(Qs + static_cast<size_t>(MQ) * P);   // [MQ][MKT + 1]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  const int h = blockIdx.y;
+  // which (sequence, 16-row tile) is this block?  tiles never straddle sequences
+  int b = -1, row0 = 0, nrows = 0;
+  {
+    int acc = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+      const int n = static_cast<int>(cu[s + 1] - cu[s]), tiles = (n + MQ - 1) / MQ;
+      if (static_cast<int>(blockIdx.x) < acc + tiles) {
+        const int k = blockIdx.x - acc;
+        b = s;
+        row0 = cu[s] + k * MQ;
+        nrows = min(MQ, n - k * MQ);
+        break;
+      }
+      acc += tiles;
+    }
+  }
+  if (b < 0) return;
+  const int qlen = static_cast<int>(cu[b + 1] - cu[b]);
+  const int pos0 = static_cast<int>(ctx[b]) - qlen + (row0 - static_cast<int>(cu[b]));     // position of the tile's first row
+  const int pos_last = pos0 + nrows - 1;
+  const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  // stage Q (bf16) once
+  for (int e = threadIdx.x; e < MQ * R; e += blockDim.x) {
+    const int r = e / R, d = e % R;
+    const float v = r < nrows ? q_full[(static_cast<size_t>(row0 + r) * heads + h) * R + d] : 0.f;
+    Qs[r * P + d] = __float2bfloat16_rn(v);
+  }
+  float m[2], l[2];
+  const float sk = sink ? sink[h] : -1e30f;
+  m[0] = m[1] = sk;
+  l[0] = l[1] = sink ? 1.f : 0.f;
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  const uint32_t* bt = block_tables + static_cast<size_t>(b) * max_blocks;
+  const int rowp[2] = {pos0 + g, pos0 + g + 8};            // positions of this lane's two rows
+  for (int j0 = key_lo; j0 <= pos_last; j0 += MKT) {
+    __syncthreads();
+    // key tile: 16-byte copies (R % 8 == 0), zero rows past the last visible key
+    const int vec = R / 8;
+    for (int e = threadIdx.x; e < MKT * vec; e += blockDim.x) {
+      const int k = e / vec, d = (e % vec) * 8, j = j0 + k;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j <= pos_last) {
+        const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
+        v = *reinterpret_cast<const uint4*>(cache + slot * R + d);
+      }
+      *reinterpret_cast<uint4*>(Ks + static_cast<size_t>(k) * P + d) = v;
+    }
+    __syncthreads();
+    // scores of keys [16 warp, 16 warp + 16)
+    float sc[2][4] = {};
+    for (int kk = 0; kk < R; kk += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * P + kk + 2 * tq);
+      a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * P + kk + 2 * tq);
+      a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * P + kk + 2 * tq + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * P + kk + 2 * tq + 8);
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        const __nv_bfloat16* kr = Ks + static_cast<size_t>(warp * 16 + nb * 8 + g) * P + kk + 2 * tq;
+        mma_bf16_16816(sc[nb], a, *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+      }
+    }
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        const int r = g + (f >> 1) * 8, kcol = warp * 16 + nb * 8 + 2 * tq + (f & 1);
+        Ss[r * (MKT + 1) + kcol] = sc[nb][f] * scale;
+      }
+    __syncthreads();
+    // the same online softmax in every warp; this lane's P entries are exactly its A fragments
+    float p[2][16];
+    float mx[2] = {-1e30f, -1e30f};
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int r = g + rr * 8;
+      const int lo = window > 0 ? max(0, rowp[rr] - window + 1) : 0;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int kcol = ks * 16 + 2 * tq + (c & 1) + (c >> 1) * 8, j = j0 + kcol;
+          const bool ok = r < nrows && j >= lo && j <= rowp[rr];
+          const float v = ok ? Ss[r * (MKT + 1) + kcol] : -1e30f;
+          p[rr][ks * 4 + c] = v;
+          mx[rr] = fmaxf(mx[rr], v);
+        }
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+    }
+    float alpha[2];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const float mn = fmaxf(m[rr], mx[rr]);
+      alpha[rr] = expf(m[rr] - mn);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float e = p[rr][i] > -1e29f ? expf(p[rr][i] - mn) : 0.f;
+        p[rr][i] = e;
+        sum += e;
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l[rr] = l[rr] * alpha[rr] + sum;
+      m[rr] = mn;
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+    }
+    // O += P V over this warp's latent columns [warp * NT * 8, +NT * 8)
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      uint32_t a[4];
+      a[0] = pack_bf16(p[0][ks * 4 + 0], p[0][ks * 4 + 1]);
+      a[1] = pack_bf16(p[1][ks * 4 + 0], p[1][ks * 4 + 1]);
+      a[2] = pack_bf16(p[0][ks * 4 + 2], p[0][ks * 4 + 3]);
+      a[3] = pack_bf16(p[1][ks * 4 + 2], p[1][ks * 4 + 3]);
+#pragma unroll
+      for (int n = 0; n < NT; n += 2) {
+        // four 8 x 8 blocks: (keys 0-7 | 8-15 of the step) x (columns d0 .. d0+7 | d0+8 .. d0+15), transposed on load
+        const int d0 = (warp * NT + n) * 8;
+        const __nv_bfloat16* src = Ks + static_cast<size_t>(ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * P + d0 + (lane >> 4) * 8;
+        uint32_t r0, r1, r2, r3;
+        const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(src));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+        mma_bf16_16816(o[n], a, r0, r1);
+        if (n + 1 < NT) mma_bf16_16816(o[n + 1], a, r2, r3);
+      }
+    }
+  }
+  const float inv[2] = {l[0] > 0.f ? 1.f / l[0] : 0.f, l[1] > 0.f ? 1.f / l[1] : 0.f};
+#pragma unroll
+  for (int n = 0; n < NT; ++n)
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int r = g + rr * 8;
+      if (r < nrows) {
+        const int d = (warp * NT + n) * 8 + 2 * tq;
+        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv[rr], o[n][rr * 2 + 1] * inv[rr]);
+        *reinterpret_cast<__nv_bfloat162*>(out + (static_cast<size_t>(row0 + r) * heads + h) * kv_rank + d) = v;
+      }
+    }
+}
+
+static bool latent_mma_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200_LATENT_MMA");       // 0: the FMA kernel for every step (A/B arm)
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+// true when the tensor-core kernel took the step
+static bool launch_latent_attn_mma(void* out, const float* q_full, const void* cache, const float* sink,
+                                   const uint32_t* cu, const uint32_t* ctx, const uint32_t* block_tables, int max_blocks,
+                                   int num_seqs, int T, int heads, int kv_rank, int rot_dim, int window, float scale,
+                                   cudaStream_t st_) {
+  const int R = kv_rank + rot_dim;
+  if (!latent_mma_enabled() || R % 16 != 0 || kv_rank % 32 != 0 || kv_rank / 32 > 16 || ((kv_rank / 32) & 1)) return false;
+  const size_t smem = static_cast<size_t>(MKT + MQ) * (R + 8) * 2 + static_cast<size_t>(MQ) * (MKT + 1) * 4;
+  if (smem > 200 * 1024) return false;
+  const dim3 grid((T + MQ - 1) / MQ + num_seqs, heads);
+#define B200_LMMA(NT)                                                                                              \
+  {                                                                                                                \
+    auto kern = latent_attn_mma_kernel<NT>;                                                                        \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));               \
+    kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q_full, (const __nv_bfloat16*)cache, sink, cu, ctx,        \
+                                   block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale);    \
+  }
+  switch (kv_rank / 32) {
+    case 2: B200_LMMA(2) break;
+    case 4: B200_LMMA(4) break;
+    case 6: B200_LMMA(6) break;
+    case 8: B200_LMMA(8) break;
+    case 10: B200_LMMA(10) break;
+    case 12: B200_LMMA(12) break;
+    case 14: B200_LMMA(14) break;
+    case 16: B200_LMMA(16) break;
+    default: return false;
+  }
+#undef B200_LMMA
+  B200_CUDA_LAUNCH_CHECK();
+  return true;
+}
+
 int latent_attn_splits(int T, int heads, int window) {
   const int nw = heads >= 8 ? 8 : (heads >= 4 ? 4 : (heads >= 2 ? 2 : 1));
   const int blocks = T * ((heads + nw - 1) / nw);
@@ -230,6 +454,11 @@ void launch_latent_attn(void* out, const float* q_full, const void* cache, const
                         int heads, int kv_rank, int rot_dim, int window, float scale, int dt, void* workspace,
                         cudaStream_t st_) {
   if (T <= 0) return;
+  // steps of many rows in bf16: the tensor-core kernel (small steps keep the split form below)
+  if (!dt && T > 2 * sm_count() / 4 &&
+      launch_latent_attn_mma(out, q_full, cache, sink, cu, ctx, block_tables, max_blocks, num_seqs, T, heads, kv_rank,
+                             rot_dim, window, scale, st_))
+    return;
   const int R = kv_rank + rot_dim, Rp = R | 1;
   const int nw = heads >= 8 ? 8 : (heads >= 4 ? 4 : (heads >= 2 ? 2 : 1));
   int key_tile = 32;
