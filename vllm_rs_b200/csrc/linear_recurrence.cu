@@ -12,7 +12,7 @@
 //                     g = exp(-exp(a_log) * softplus(a + dt_bias)).  state [slots, heads, dim, vdim].
 //   ssd_scan        : per head, S [nstate, vdim]:  dt = softplus(dt_raw + dt_bias);  S <- exp(-exp(a_log) dt) S + dt B x^T;
 //                     y = S^T C + D x.  state [slots, heads, nstate, vdim].
-// In both scans four lanes share one column of S (one value channel), each holding every fourth row in registers,
+// In both scans eight lanes share one column of S (one value channel), each holding every eighth row in registers,
 // and walk the sequence's tokens in order: the exact recurrence, no chunked reformulation, so a portion boundary
 // cannot change the arithmetic.
 #include "../../include/b200_vllm.h"
@@ -87,9 +87,9 @@ __global__ void short_conv_state_kernel(const float* __restrict__ x, int ldx, fl
 }
 
 constexpr int kChunk = 8;          // tokens staged in shared memory per pass
-constexpr int kRowSplit = 4;       // lanes that share one column of S (each holds every 4th row)
+constexpr int kRowSplit = 8;       // lanes that share one column of S (each holds every 8th row)
 
-// grid = (column blocks, heads, sequences); block = 128 threads = 32 columns x kRowSplit lanes.  DK = compile-time
+// grid = (column blocks, heads, sequences); block = 128 threads = 16 columns x kRowSplit lanes.  DK = compile-time
 // bound of `dim`; a lane holds the rows i = j * kRowSplit + part of its column.
 template <int DK>
 __global__ void __launch_bounds__(128)

@@ -179,12 +179,23 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
+               "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 grouped_linear_mma_kernel(void* __restrict__ out_, const __nv_bfloat16* __restrict__ a,
                           const __nv_bfloat16* __restrict__ w, const int32_t* __restrict__ off,
                           const int32_t* __restrict__ pair_of_slot, int top, int E, int K, int N) {
-  __shared__ __align__(16) __nv_bfloat16 As[TM][MP], W0[MN][MP], W1[GATED ? MN : 1][MP];
+  // two stages: the 16-byte asynchronous copies of K chunk i + 1 run under the MMAs of chunk i
+  __shared__ __align__(16) __nv_bfloat16 As[2][TM][MP], W0[2][MN][MP], W1[2][GATED ? MN : 1][MP];
   __shared__ size_t arow[TM];
   int e, s0, rows;
   if (!find_tile(off, E, blockIdx.x, &e, &s0, &rows)) return;
@@ -195,40 +206,50 @@ grouped_linear_mma_kernel(void* __restrict__ out_, const __nv_bfloat16* __restri
     const int slot = s0 + min(static_cast<int>(threadIdx.x), rows - 1);
     arow[threadIdx.x] = GATED ? static_cast<size_t>(pair_of_slot[slot] / top) : static_cast<size_t>(slot);
   }
+  __syncthreads();
   float acc0[2][2][4] = {}, acc1[2][2][4] = {};      // [row half][8-column block][fragment]
-  const bool vec = (K % 8) == 0;
-  for (int k0 = 0; k0 < K; k0 += MK) {
-    __syncthreads();
-    if (vec) {          // 16-byte copies (K % 8 == 0 keeps every row start 16-byte aligned)
-      for (int i = threadIdx.x; i < TM * (MK / 8); i += 128) {
-        const int r = i / (MK / 8), k = (i % (MK / 8)) * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < rows && k0 + k < K) v = *reinterpret_cast<const uint4*>(a + arow[r] * K + k0 + k);
-        *reinterpret_cast<uint4*>(&As[r][k]) = v;
+  const bool vec = (K % 8) == 0;                     // every row start is 16-byte aligned
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  auto load_async = [&](int st, int k0) {
+    for (int i = threadIdx.x; i < TM * (MK / 8); i += 128) {
+      const int r = i / (MK / 8), k = (i % (MK / 8)) * 8;
+      if (r < rows && k0 + k < K) cp_async16(&As[st][r][k], a + arow[r] * K + k0 + k);
+      else *reinterpret_cast<uint4*>(&As[st][r][k]) = zero4;
+    }
+    for (int i = threadIdx.x; i < MN * (MK / 8); i += 128) {
+      const int n = i / (MK / 8), k = (i % (MK / 8)) * 8;
+      const bool ok = n0 + n < N && k0 + k < K;
+      if (ok) cp_async16(&W0[st][n][k], we + static_cast<size_t>(n0 + n) * K + k0 + k);
+      else *reinterpret_cast<uint4*>(&W0[st][n][k]) = zero4;
+      if (GATED) {
+        if (ok) cp_async16(&W1[st][n][k], we + static_cast<size_t>(N + n0 + n) * K + k0 + k);
+        else *reinterpret_cast<uint4*>(&W1[st][n][k]) = zero4;
       }
-      for (int i = threadIdx.x; i < MN * (MK / 8); i += 128) {
-        const int n = i / (MK / 8), k = (i % (MK / 8)) * 8;
-        const bool ok = n0 + n < N && k0 + k < K;
-        uint4 v = make_uint4(0, 0, 0, 0), u = make_uint4(0, 0, 0, 0);
-        if (ok) v = *reinterpret_cast<const uint4*>(we + static_cast<size_t>(n0 + n) * K + k0 + k);
-        *reinterpret_cast<uint4*>(&W0[n][k]) = v;
-        if (GATED) {
-          if (ok) u = *reinterpret_cast<const uint4*>(we + static_cast<size_t>(N + n0 + n) * K + k0 + k);
-          *reinterpret_cast<uint4*>(&W1[n][k]) = u;
-        }
-      }
+    }
+    cp_async_commit();
+  };
+  auto load_plain = [&](int st, int k0) {
+    const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
+    for (int i = threadIdx.x; i < TM * MK; i += 128) {
+      const int r = i / MK, k = i % MK;
+      As[st][r][k] = (r < rows && k0 + k < K) ? a[arow[r] * K + k0 + k] : zero;
+    }
+    for (int i = threadIdx.x; i < MN * MK; i += 128) {
+      const int n = i / MK, k = i % MK;
+      const bool ok = n0 + n < N && k0 + k < K;
+      W0[st][n][k] = ok ? we[static_cast<size_t>(n0 + n) * K + k0 + k] : zero;
+      if (GATED) W1[st][n][k] = ok ? we[static_cast<size_t>(N + n0 + n) * K + k0 + k] : zero;
+    }
+  };
+  int st = 0;
+  if (vec) load_async(0, 0);
+  for (int k0 = 0; k0 < K; k0 += MK, st ^= 1) {
+    if (vec) {
+      const bool more = k0 + MK < K;
+      if (more) load_async(st ^ 1, k0 + MK);
+      if (more) cp_async_wait<1>(); else cp_async_wait<0>();
     } else {
-      const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
-      for (int i = threadIdx.x; i < TM * MK; i += 128) {
-        const int r = i / MK, k = i % MK;
-        As[r][k] = (r < rows && k0 + k < K) ? a[arow[r] * K + k0 + k] : zero;
-      }
-      for (int i = threadIdx.x; i < MN * MK; i += 128) {
-        const int n = i / MK, k = i % MK;
-        const bool ok = n0 + n < N && k0 + k < K;
-        W0[n][k] = ok ? we[static_cast<size_t>(n0 + n) * K + k0 + k] : zero;
-        if (GATED) W1[n][k] = ok ? we[static_cast<size_t>(N + n0 + n) * K + k0 + k] : zero;
-      }
+      load_plain(st, k0);
     }
     __syncthreads();
 #pragma unroll
@@ -236,27 +257,28 @@ grouped_linear_mma_kernel(void* __restrict__ out_, const __nv_bfloat16* __restri
       uint32_t af[2][4];
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
-        af[hf][0] = *reinterpret_cast<const uint32_t*>(&As[hf * 16 + g][kk + 2 * tq]);
-        af[hf][1] = *reinterpret_cast<const uint32_t*>(&As[hf * 16 + g + 8][kk + 2 * tq]);
-        af[hf][2] = *reinterpret_cast<const uint32_t*>(&As[hf * 16 + g][kk + 2 * tq + 8]);
-        af[hf][3] = *reinterpret_cast<const uint32_t*>(&As[hf * 16 + g + 8][kk + 2 * tq + 8]);
+        af[hf][0] = *reinterpret_cast<const uint32_t*>(&As[st][hf * 16 + g][kk + 2 * tq]);
+        af[hf][1] = *reinterpret_cast<const uint32_t*>(&As[st][hf * 16 + g + 8][kk + 2 * tq]);
+        af[hf][2] = *reinterpret_cast<const uint32_t*>(&As[st][hf * 16 + g][kk + 2 * tq + 8]);
+        af[hf][3] = *reinterpret_cast<const uint32_t*>(&As[st][hf * 16 + g + 8][kk + 2 * tq + 8]);
       }
 #pragma unroll
       for (int nb = 0; nb < 2; ++nb) {
         const int n = warp * 16 + nb * 8 + g;
         uint32_t bf[2];
-        bf[0] = *reinterpret_cast<const uint32_t*>(&W0[n][kk + 2 * tq]);
-        bf[1] = *reinterpret_cast<const uint32_t*>(&W0[n][kk + 2 * tq + 8]);
+        bf[0] = *reinterpret_cast<const uint32_t*>(&W0[st][n][kk + 2 * tq]);
+        bf[1] = *reinterpret_cast<const uint32_t*>(&W0[st][n][kk + 2 * tq + 8]);
         mma_bf16(acc0[0][nb], af[0], bf);
         mma_bf16(acc0[1][nb], af[1], bf);
         if (GATED) {
-          bf[0] = *reinterpret_cast<const uint32_t*>(&W1[n][kk + 2 * tq]);
-          bf[1] = *reinterpret_cast<const uint32_t*>(&W1[n][kk + 2 * tq + 8]);
+          bf[0] = *reinterpret_cast<const uint32_t*>(&W1[st][n][kk + 2 * tq]);
+          bf[1] = *reinterpret_cast<const uint32_t*>(&W1[st][n][kk + 2 * tq + 8]);
           mma_bf16(acc1[0][nb], af[0], bf);
           mma_bf16(acc1[1][nb], af[1], bf);
         }
       }
     }
+    __syncthreads();          // the stage is free before the next round's copies land in it
   }
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf)
