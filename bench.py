@@ -78,6 +78,8 @@ def parse():
     ap.add_argument("--py-step", action="store_true",
                     help="e2e: drive the step from Python over the individual C symbols instead of b200_engine_step")
     ap.add_argument("--size", default="w2048,w4096", help="--config fidasun: layer sizes, comma separated")
+    ap.add_argument("--dense-arm", action="store_true",
+                    help="--config fidasun: also time the dense fp16 plan of equal size now (time-limited process)")
     ap.add_argument("--prefill-tokens", type=int, default=8192,
                     help="N = 1: also time the prefill legs (0 = skip); the AWQ chunk has this many tokens")
     return ap.parse_args()
@@ -761,7 +763,8 @@ def run_b200(args):
         launches0 = _lib.lib().b200_launch_count()
         with ClockSampler(cx.local) as clk:
             sizes = [bench_hybrid.run(sz, layers=args.layers or 4, prefill=4096, batch=args.batch, ctx=2048,
-                                      reps=max(args.steps // 4, 3)) for sz in args.size.split(",")]
+                                      reps=max(args.steps // 4, 3), dense=args.dense_arm)
+                     for sz in args.size.split(",")]
         first = sizes[0]
         line = {"metric": "decode tokens/s (Fidasun hybrid decoder, random weights)",
                 "value": first["fidasun"]["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": max(args.steps // 4, 3) * 4,

@@ -86,7 +86,8 @@ __global__ void short_conv_state_kernel(const float* __restrict__ x, int ldx, fl
   for (int j = 0; j < P; ++j) sp[static_cast<size_t>(j) * C] = keep[j];
 }
 
-constexpr int kChunk = 8;          // tokens staged in shared memory per pass
+// tokens staged in shared memory per pass (static shared memory stays under 48 KB for the widest state)
+constexpr int chunk_for(int rows) { return rows > 128 ? 16 : 32; }
 constexpr int kRowSplit = 8;       // lanes that share one column of S (each holds every 8th row)
 
 // grid = (column blocks, heads, sequences); block = 128 threads = 16 columns x kRowSplit lanes.  DK = compile-time
@@ -99,7 +100,7 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
                   const float* __restrict__ dt_bias, float* __restrict__ state, const int32_t* __restrict__ slots,
                   const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx, int heads, int kv_heads, int dim,
                   int vdim) {
-  constexpr int RS = kRowSplit, NR = DK / RS;
+  constexpr int RS = kRowSplit, NR = DK / RS, kChunk = chunk_for(DK);
   __shared__ float ks[kChunk][DK], qs[kChunk][DK], gs[kChunk], bs[kChunk];
   const int h = blockIdx.y, b = blockIdx.z;
   const int part = threadIdx.x % RS;
@@ -143,7 +144,10 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
       }
     }
     __syncthreads();
+    float vnext = live ? v[static_cast<size_t>(c0) * ld + h * vdim + col] : 0.f;
     for (int r = 0; r < n; ++r) {          // every lane runs the shuffles; dead columns carry zeros
+      const float vv = vnext;              // the next token's value is fetched under this token's arithmetic
+      if (r + 1 < n && live) vnext = v[static_cast<size_t>(c0 + r + 1) * ld + h * vdim + col];
       const float g = gs[r];
       float d0 = 0.f, d1 = 0.f;
 #pragma unroll
@@ -158,7 +162,6 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
       float dot = d0 + d1;
 #pragma unroll
       for (int o = 1; o < RS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float vv = live ? v[static_cast<size_t>(c0 + r) * ld + h * vdim + col] : 0.f;
       const float u = bs[r] * (vv - dot);
       float o0 = 0.f, o1 = 0.f;
 #pragma unroll
@@ -192,7 +195,7 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
                 const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ d_skip,
                 float* __restrict__ state, const int32_t* __restrict__ slots, const uint32_t* __restrict__ cu,
                 const uint32_t* __restrict__ ctx, int heads, int groups, int nstate, int vdim) {
-  constexpr int RS = kRowSplit, NR = NS / RS;
+  constexpr int RS = kRowSplit, NR = NS / RS, kChunk = chunk_for(NS);
   __shared__ float Bs[kChunk][NS], Cs[kChunk][NS], dts[kChunk], das[kChunk];
   const int h = blockIdx.y, b = blockIdx.z;
   const int part = threadIdx.x % RS;
@@ -224,8 +227,10 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
       das[threadIdx.x] = expf(neg_a * dt);
     }
     __syncthreads();
+    float xnext = live ? x[static_cast<size_t>(c0) * ld + h * vdim + col] : 0.f;
     for (int r = 0; r < n; ++r) {
-      const float xv = live ? x[static_cast<size_t>(c0 + r) * ld + h * vdim + col] : 0.f;
+      const float xv = xnext;              // the next token's input is fetched under this token's arithmetic
+      if (r + 1 < n && live) xnext = x[static_cast<size_t>(c0 + r + 1) * ld + h * vdim + col];
       const float a = das[r], dx = dts[r] * xv;
       float y0 = 0.f, y1 = 0.f;
 #pragma unroll
