@@ -232,24 +232,34 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-// NT = n-tiles (8 latent columns each) per warp = kv_rank / 32
-template <int NT>
+// NT = n-tiles (8 latent columns each) per warp = kv_rank / 32.  HROWS = false: the 16 MMA rows are 16 consecutive token
+// rows of one head (prompt portions).  HROWS = true (steps of few rows, decoding): the 16 rows are 16 HEADS of one
+// token -- all heads share the key rows, so one pass over the cache serves them all -- and blockIdx.z owns a
+// contiguous run of key tiles; with nsplit > 1 the unnormalised parts go to part_o / part_ml and
+// latent_attn_merge_kernel finishes the softmax (it adds the sink).
+template <int NT, bool HROWS>
 __global__ void __launch_bounds__(128)
 latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ q_full,
                        const __nv_bfloat16* __restrict__ cache, const float* __restrict__ sink,
                        const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
                        const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_rank,
-                       int rot_dim, int window, float scale) {
+                       int rot_dim, int window, float scale, int nsplit, float* __restrict__ part_o,
+                       float* __restrict__ part_ml) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int R = kv_rank + rot_dim, P = R + 8;             // P: row pitch in bf16 elements (16-byte multiple)
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [MKT][P]
   __nv_bfloat16* Qs = Ks + static_cast<size_t>(MKT) * P;                    // [MQ][P]
   float* Ss = reinterpret_cast<float*>(Qs + static_cast<size_t>(MQ) * P);   // [MQ][MKT + 1]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
-  const int h = blockIdx.y;
-  // which (sequence, 16-row tile) is this block?  tiles never straddle sequences
-  int b = -1, row0 = 0, nrows = 0;
-  {
+  // which rows does this block own?
+  int b = -1, row0 = 0, nrows = 0, h = blockIdx.y, pos0 = 0;
+  if (HROWS) {                                   // one token, heads [16 blockIdx.y, +16)
+    row0 = blockIdx.x;
+    b = seq_of_row(cu, num_seqs, row0);
+    h = blockIdx.y * MQ;
+    nrows = min(MQ, heads - h);
+    pos0 = static_cast<int>(ctx[b]) - static_cast<int>(cu[b + 1] - cu[b]) + (row0 - static_cast<int>(cu[b]));
+  } else {                                       // 16 token rows of one sequence (tiles never straddle sequences)
     int acc = 0;
     for (int s = 0; s < num_seqs; ++s) {
       const int n = static_cast<int>(cu[s + 1] - cu[s]), tiles = (n + MQ - 1) / MQ;
@@ -262,35 +272,43 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
       }
       acc += tiles;
     }
+    if (b < 0) return;
+    pos0 = static_cast<int>(ctx[b]) - static_cast<int>(cu[b + 1] - cu[b]) + (row0 - static_cast<int>(cu[b]));
   }
-  if (b < 0) return;
-  const int qlen = static_cast<int>(cu[b + 1] - cu[b]);
-  const int pos0 = static_cast<int>(ctx[b]) - qlen + (row0 - static_cast<int>(cu[b]));     // position of the tile's first row
-  const int pos_last = pos0 + nrows - 1;
+  const int pos_last = HROWS ? pos0 : pos0 + nrows - 1;
   const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
   // stage Q (bf16) once
   for (int e = threadIdx.x; e < MQ * R; e += blockDim.x) {
     const int r = e / R, d = e % R;
-    const float v = r < nrows ? q_full[(static_cast<size_t>(row0 + r) * heads + h) * R + d] : 0.f;
+    const size_t qrow = HROWS ? static_cast<size_t>(row0) * heads + h + r : static_cast<size_t>(row0 + r) * heads + h;
+    const float v = r < nrows ? q_full[qrow * R + d] : 0.f;
     Qs[r * P + d] = __float2bfloat16_rn(v);
   }
   float m[2], l[2];
-  const float sk = sink ? sink[h] : -1e30f;
-  m[0] = m[1] = sk;
-  l[0] = l[1] = sink ? 1.f : 0.f;
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int hh = HROWS ? min(h + g + rr * 8, heads - 1) : h;
+    const bool with_sink = sink && nsplit == 1;          // split runs add the sink when the parts are merged
+    m[rr] = with_sink ? sink[hh] : -1e30f;
+    l[rr] = with_sink ? 1.f : 0.f;
+  }
   float o[NT][4];
 #pragma unroll
   for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   const uint32_t* bt = block_tables + static_cast<size_t>(b) * max_blocks;
-  const int rowp[2] = {pos0 + g, pos0 + g + 8};            // positions of this lane's two rows
-  for (int j0 = key_lo; j0 <= pos_last; j0 += MKT) {
+  const int rowp[2] = {HROWS ? pos0 : pos0 + g, HROWS ? pos0 : pos0 + g + 8};   // positions of this lane's two rows
+  // the run of key tiles of this block (nsplit == 1: all of them)
+  const int ntiles = (pos_last - key_lo + MKT) / MKT, per = (ntiles + nsplit - 1) / nsplit;
+  const int first = key_lo + static_cast<int>(blockIdx.z) * per * MKT;
+  const int last_key = min(pos_last, first + per * MKT - 1);
+  for (int j0 = first; j0 <= last_key; j0 += MKT) {
     __syncthreads();
     // key tile: 16-byte copies (R % 8 == 0), zero rows past the last visible key
     const int vec = R / 8;
     for (int e = threadIdx.x; e < MKT * vec; e += blockDim.x) {
       const int k = e / vec, d = (e % vec) * 8, j = j0 + k;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (j <= pos_last) {
+      if (j <= last_key) {
         const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
         v = *reinterpret_cast<const uint4*>(cache + slot * R + d);
       }
@@ -331,7 +349,7 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int kcol = ks * 16 + 2 * tq + (c & 1) + (c >> 1) * 8, j = j0 + kcol;
-          const bool ok = r < nrows && j >= lo && j <= rowp[rr];
+          const bool ok = r < nrows && j >= lo && j <= rowp[rr] && j <= last_key;
           const float v = ok ? Ss[r * (MKT + 1) + kcol] : -1e30f;
           p[rr][ks * 4 + c] = v;
           mx[rr] = fmaxf(mx[rr], v);
@@ -384,16 +402,31 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
   }
   const float inv[2] = {l[0] > 0.f ? 1.f / l[0] : 0.f, l[1] > 0.f ? 1.f / l[1] : 0.f};
 #pragma unroll
-  for (int n = 0; n < NT; ++n)
+  for (int rr = 0; rr < 2; ++rr) {
+    const int r = g + rr * 8;
+    if (r >= nrows) continue;
+    const size_t orow = HROWS ? static_cast<size_t>(row0) * heads + h + r : static_cast<size_t>(row0 + r) * heads + h;
+    if (nsplit == 1) {
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      const int r = g + rr * 8;
-      if (r < nrows) {
+      for (int n = 0; n < NT; ++n) {
         const int d = (warp * NT + n) * 8 + 2 * tq;
         __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv[rr], o[n][rr * 2 + 1] * inv[rr]);
-        *reinterpret_cast<__nv_bfloat162*>(out + (static_cast<size_t>(row0 + r) * heads + h) * kv_rank + d) = v;
+        *reinterpret_cast<__nv_bfloat162*>(out + orow * kv_rank + d) = v;
+      }
+    } else {
+      const size_t pi = orow * nsplit + blockIdx.z;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int d = (warp * NT + n) * 8 + 2 * tq;
+        part_o[pi * kv_rank + d] = o[n][rr * 2];
+        part_o[pi * kv_rank + d + 1] = o[n][rr * 2 + 1];
+      }
+      if (warp == 0 && tq == 0) {
+        part_ml[pi * 2] = m[rr];
+        part_ml[pi * 2 + 1] = l[rr];
       }
     }
+  }
 }
 
 static bool latent_mma_enabled() {
@@ -404,23 +437,41 @@ static bool latent_mma_enabled() {
   }
   return v == 1;
 }
-// true when the tensor-core kernel took the step
+static bool latent_mma_shape_ok(int kv_rank, int rot_dim) {
+  const int R = kv_rank + rot_dim;
+  if (R % 16 != 0 || kv_rank % 64 != 0 || kv_rank > 512) return false;
+  return static_cast<size_t>(MKT + MQ) * (R + 8) * 2 + static_cast<size_t>(MQ) * (MKT + 1) * 4 <= 200 * 1024;
+}
+// key splits of the heads-as-rows form: two blocks per SM, at most one split per key tile of the window, at most 16
+static int latent_attn_mma_splits(int T, int heads, int window) {
+  const int blocks = T * ((heads + MQ - 1) / MQ);
+  int n = (2 * sm_count() + blocks - 1) / blocks;
+  if (window > 0) n = std::min(n, (window + MKT - 1) / MKT);
+  return std::max(1, std::min(n, 16));
+}
+// true when the tensor-core kernel took the step.  hrows: steps of few rows (heads as MMA rows, keys split).
 static bool launch_latent_attn_mma(void* out, const float* q_full, const void* cache, const float* sink,
                                    const uint32_t* cu, const uint32_t* ctx, const uint32_t* block_tables, int max_blocks,
                                    int num_seqs, int T, int heads, int kv_rank, int rot_dim, int window, float scale,
-                                   cudaStream_t st_) {
+                                   bool hrows, void* workspace, cudaStream_t st_) {
   const int R = kv_rank + rot_dim;
-  if (!latent_mma_enabled() || R % 16 != 0 || kv_rank % 32 != 0 || kv_rank / 32 > 16 || ((kv_rank / 32) & 1)) return false;
+  if (!latent_mma_enabled() || !latent_mma_shape_ok(kv_rank, rot_dim)) return false;
   const size_t smem = static_cast<size_t>(MKT + MQ) * (R + 8) * 2 + static_cast<size_t>(MQ) * (MKT + 1) * 4;
-  if (smem > 200 * 1024) return false;
-  const dim3 grid((T + MQ - 1) / MQ + num_seqs, heads);
-#define B200_LMMA(NT)                                                                                              \
+  const int nsplit = hrows && workspace ? latent_attn_mma_splits(T, heads, window) : 1;
+  float* part_o = reinterpret_cast<float*>(workspace);
+  float* part_ml = part_o ? part_o + static_cast<size_t>(T) * heads * nsplit * kv_rank : nullptr;
+  const dim3 grid = hrows ? dim3(T, (heads + MQ - 1) / MQ, nsplit) : dim3((T + MQ - 1) / MQ + num_seqs, heads, 1);
+#define B200_LMMA2(NT, HR)                                                                                        \
   {                                                                                                                \
-    auto kern = latent_attn_mma_kernel<NT>;                                                                        \
+    auto kern = latent_attn_mma_kernel<NT, HR>;                                                                    \
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));               \
     kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q_full, (const __nv_bfloat16*)cache, sink, cu, ctx,        \
-                                   block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale);    \
+                                   block_tables, max_blocks, num_seqs, heads, kv_rank, rot_dim, window, scale,     \
+                                   nsplit, part_o, part_ml);                                                       \
   }
+#define B200_LMMA(NT)                 \
+  if (hrows) B200_LMMA2(NT, true)     \
+  else B200_LMMA2(NT, false)
   switch (kv_rank / 32) {
     case 2: B200_LMMA(2) break;
     case 4: B200_LMMA(4) break;
@@ -433,7 +484,13 @@ static bool launch_latent_attn_mma(void* out, const float* q_full, const void* c
     default: return false;
   }
 #undef B200_LMMA
+#undef B200_LMMA2
   B200_CUDA_LAUNCH_CHECK();
+  if (nsplit > 1) {
+    latent_attn_merge_kernel<__nv_bfloat16><<<T * heads, kv_rank >= 256 ? 256 : 128, 0, st_>>>(
+        (__nv_bfloat16*)out, part_o, part_ml, sink, heads, kv_rank, nsplit);
+    B200_CUDA_LAUNCH_CHECK();
+  }
   return true;
 }
 
@@ -445,7 +502,7 @@ int latent_attn_splits(int T, int heads, int window) {
   return std::max(1, std::min(n, 16));
 }
 size_t latent_attn_workspace_bytes(int T, int heads, int kv_rank, int window) {
-  const int n = latent_attn_splits(T, heads, window);
+  const int n = std::max(latent_attn_splits(T, heads, window), latent_attn_mma_splits(T, heads, window));
   return n == 1 ? 0 : static_cast<size_t>(T) * heads * n * (kv_rank + 2) * 4;
 }
 
@@ -455,9 +512,8 @@ void launch_latent_attn(void* out, const float* q_full, const void* cache, const
                         cudaStream_t st_) {
   if (T <= 0) return;
   // steps of many rows in bf16: the tensor-core kernel (small steps keep the split form below)
-  if (!dt && T > 2 * sm_count() / 4 &&
-      launch_latent_attn_mma(out, q_full, cache, sink, cu, ctx, block_tables, max_blocks, num_seqs, T, heads, kv_rank,
-                             rot_dim, window, scale, st_))
+  if (!dt && launch_latent_attn_mma(out, q_full, cache, sink, cu, ctx, block_tables, max_blocks, num_seqs, T, heads,
+                                    kv_rank, rot_dim, window, scale, /*hrows=*/T <= 2 * sm_count() / 4, workspace, st_))
     return;
   const int R = kv_rank + rot_dim, Rp = R | 1;
   const int nw = heads >= 8 ? 8 : (heads >= 4 ? 4 : (heads >= 2 ? 2 : 1));
