@@ -121,3 +121,9 @@ def test_plain_model_invariants():
     a, b = R.forward(one, w1, t).numpy(), R.forward(one, w1, t2).numpy()
     assert np.abs(a[13] - b[13]).max() > 1e-6 and np.abs(a[14] - b[14]).max() == 0.0      # 13 sees 10, 14 does not
     assert len(full_cfg()["layers"]) == 5
+
+
+def test_command_line_lists_the_architectures(capsys):
+    from vllm_rs_b200.__main__ import main
+    assert main(["models"]) == 0
+    assert "Fidasun" in capsys.readouterr().out.split()

@@ -26,9 +26,9 @@ def _generate(a) -> int:
         build.build(verbose=False, target="hybrid" if arch == "Fidasun" else "full")
     prompts = [[int(x) for x in p.split(",") if x.strip()] for p in a.prompt_ids]
     longest = max(len(p) for p in prompts) + a.max_new_tokens
-    per_seq = (longest + 63) // 64 + 1
+    per_seq = (longest + 63) // 64 + 2
     n = max(len(prompts), 1)
-    num_blocks = per_seq * n
+    num_blocks = per_seq * n + 2          # the block manager keeps a spare block per appending sequence
     dtype = getattr(torch, a.dtype) if a.dtype else None
     runner = models.build_runner(cfg, tensors, dtype=dtype, device="cuda", num_blocks=num_blocks,
                                  max_blocks_per_seq=per_seq, max_seqs=max(n, 5), max_tokens=a.chunk,

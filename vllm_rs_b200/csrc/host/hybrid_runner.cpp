@@ -61,8 +61,7 @@ struct b200_hybrid {
   void* moe_ws = nullptr;
   float* sh = nullptr;         // [T, 2 shared_ff] fp32
   void* sha = nullptr;         // [T, shared_ff] operand dtype
-  float* xr = nullptr;         // unused rows of the stream gathered for the head: norm reads x through out_rows
-  void* hr = nullptr;          // [R, width]
+  void* hr = nullptr;          // [R, width] final norm of the rows whose logits are wanted (read from x through out_rows)
   float* logits = nullptr;     // [R, vocab]
   // device staging of the host entry point
   uint32_t *s_ids = nullptr, *s_cu = nullptr, *s_ctx = nullptr, *s_bt = nullptr, *s_rows = nullptr, *s_out = nullptr;
@@ -274,7 +273,6 @@ static void mixer_latent(b200_hybrid* r, const b200_hybrid_layer& l, const int64
                          cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, R = l.kv_rank + l.rot_dim, n_in = in_rows(l);
-  const size_t es = c.dt ? 4 : 2;
   gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
   launch_latent_prep(r->proj, n_in, r->opa, r->aux, l.kv_cache, (const float*)l.latent_norm_w, l.rot_freq, l.rot_mag,
                      positions, slots, T, H, l.dim, l.rot_dim, l.rot_dims, l.kv_rank, c.norm_eps, c.dt, st);
@@ -296,7 +294,6 @@ static void mixer_latent(b200_hybrid* r, const b200_hybrid_layer& l, const int64
     o_in = r->opa;
   }
   gemm_f32out(o_in, H * l.vdim, 0, l.w_o, H * l.vdim, 0, r->x, c.width, 0, T, c.width, H * l.vdim, 1, 1.f, 0, c.dt, st);
-  (void)es;
 }
 
 static void mixer_delta(b200_hybrid* r, const b200_hybrid_layer& l, const uint32_t* cu, const uint32_t* ctx,
