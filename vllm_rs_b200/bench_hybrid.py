@@ -230,7 +230,7 @@ def run(size="w2048", layers=4, prefill=4096, batch=32, ctx=2048, reps=5, dense=
     # ---- the dense fp16 LLaMA plan at equal width / depth / active feed-forward size.  At these shapes that plan did
     # not return in three of eight runs (in this process or one of its own; the GPU kept answering, the cause is not
     # found), so it runs only when asked for (--dense-arm), in a process of its own with a time limit; otherwise the
-    # line carries the numbers of a run in which it answered (profiles/r3_b_bench_fidasun_<size>.json).
+    # line carries the numbers of a run in which it answered (profiles/hy_b_bench_fidasun_<size>.json).
     import subprocess
     import sys
     root = Path(__file__).resolve().parent.parent
@@ -246,7 +246,7 @@ def run(size="w2048", layers=4, prefill=4096, batch=32, ctx=2048, reps=5, dense=
     else:
         res["llama_fp16"] = {"unavailable": "not run (ask with --dense-arm): this arm has stalled at these shapes"}
     if "unavailable" in res["llama_fp16"]:
-        rec = root / "profiles" / f"r3_b_bench_fidasun_{size}.json"
+        rec = root / "profiles" / f"hy_b_bench_fidasun_{size}.json"
         if rec.exists() and (layers, prefill, batch, ctx) == (4, 4096, 32, 2048):
             res["llama_fp16"]["recorded"] = json.loads(rec.read_text())["sizes"][0]["llama_fp16"]
             res["llama_fp16"]["recorded_in"] = f"profiles/{rec.name}"
