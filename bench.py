@@ -94,7 +94,7 @@ def measured_peaks():
 
 
 def measured_traffic(kernel: str, key: str):
-    """dram bytes (read + write) of one launch from THIS round's committed `ncu --set full` capture
+    """dram bytes (read + write) of one launch from the committed `ncu --set full` capture
     (profiles/r2_traffic.json: {kernel: {shape key: bytes, "source": file}}); None when no capture matches."""
     p = ROOT / "profiles" / "r2_traffic.json"
     if not p.exists():

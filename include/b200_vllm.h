@@ -104,7 +104,7 @@ void b200_gemm_half_q_half_alt(const void* a, const uint32_t* qweight, const uin
                                int32_t k, int32_t bits, int64_t stream);
 void b200_gemm_half_q_half_alt_release(void);
 /* General entry: bits in {4,8}, qfmt AWQ/GPTQ, optional bias[n] (fp16, may be NULL),
- * epilogue flag.  variant: 0 = auto by m, 1 = flat GEMV (CUDA cores), 2 = tcgen05 (round-1 decode kernel for m <= 64),
+ * epilogue flag.  variant: 0 = auto by m, 1 = flat GEMV (CUDA cores), 2 = tcgen05 (tile-split decode kernel for m <= 64),
  * 3 = tcgen05 with a single K split (direct store, workspace untouched; prefill),
  * 4 = the general tcgen05 kernel even for decode shapes (A/B testing),
  * 5 = the stream-K tcgen05 decode kernel (m <= 32, k % 128 == 0, group_size = 128 * 2^j). */

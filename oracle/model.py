@@ -2,14 +2,14 @@
 
 TEST INFRASTRUCTURE (see oracle/__init__.py).  Restates, op by op,
 
-  /root/reference/src/models/llama.rs:107-131,269-321        decoder layer / forward_inner
-  /root/reference/src/models/layers/attention.rs:648-839     Attention::forward_ext
-  /root/reference/src/models/layers/mlp.rs:451-469           MLP::forward
-  /root/reference/src/models/layers/others.rs:11-66          NormX / RmsNorm
-  /root/reference/src/models/layers/rotary_emb.rs:32-73      cos/sin tables (f32 math, cast)
-  /root/reference/src/models/layers/rotary_emb.rs:208-278    llama3 rope scaling
-  /root/reference/src/utils/kvcache_allocator.rs:150-173     cache layout L2 [nb, bs, Hkv, D]
-  /root/reference/src/core/runner.rs:1243-1388               decode metadata semantics
+  src/models/llama.rs:107-131,269-321        decoder layer / forward_inner
+  src/models/layers/attention.rs:648-839     Attention::forward_ext
+  src/models/layers/mlp.rs:451-469           MLP::forward
+  src/models/layers/others.rs:11-66          NormX / RmsNorm
+  src/models/layers/rotary_emb.rs:32-73      cos/sin tables (f32 math, cast)
+  src/models/layers/rotary_emb.rs:208-278    llama3 rope scaling
+  src/utils/kvcache_allocator.rs:150-173     cache layout L2 [nb, bs, Hkv, D]
+  src/core/runner.rs:1243-1388               decode metadata semantics
 
 Arithmetic model: tensors the reference materialises in the model dtype are rounded to fp16
 at the same points (linear outputs, RoPE outputs, attention output, residual adds, norm
@@ -125,7 +125,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def normx(x: torch.Tensor, w: torch.Tensor, eps: float, norm_dtype=None) -> torch.Tensor:
-    """NormX::forward (/root/reference/src/models/layers/others.rs:11-30) with the norm weight loaded by
+    """NormX::forward (src/models/layers/others.rs:11-30) with the norm weight loaded by
     rms_norm_sharded (others.rs:43-66).  llama.rs builds its norms in the model dtype (norm_dtype None): the fused
     RmsNorm runs on the fp16 tensor -- fp32 inside, ONE rounding of x * rsqrt(mean(x^2) + eps) * w to fp16.
     qwen3.rs:83,95,261 (Qwen2 / Qwen3) builds them with DType::F32: the weight is cast to f32 at load (exact:

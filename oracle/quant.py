@@ -1,7 +1,7 @@
 """AWQ / GPTQ checkpoint formats: pack, unpack, dequantise (numpy).
 
 TEST INFRASTRUCTURE (see oracle/__init__.py).  Formats as implied by the reference loader
-/root/reference/src/models/layers/wna16.rs:56-83,127-152 (tensor names / shapes / shard dims)
+src/models/layers/wna16.rs:56-83,127-152 (tensor names / shapes / shard dims)
 and the public AutoGPTQ / AutoAWQ packing:
 
   GPTQ  qweight i32 [K/pack, N]  element (k,n) = (w[k//pack, n] >> bits*(k%pack)) & mask

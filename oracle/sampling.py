@@ -1,7 +1,7 @@
 """Sampling oracle.  TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).
 
 Restates, in numpy / pure Python:
-  * LogitsProcessor::get_strategy                 (/root/reference/src/utils/logits_processor.rs:48-70)
+  * LogitsProcessor::get_strategy                 (src/utils/logits_processor.rs:48-70)
   * the (k, p, t) the CUDA sampler is called with (logits_processor.rs:199-231)
   * sample_topk_topp / sample_topk / sample_topp  (logits_processor.rs:84-196; the CPU branch, which is
     the only source-visible definition of "top-k then top-p then multinomial")

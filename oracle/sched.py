@@ -2,13 +2,13 @@
 
 TEST INFRASTRUCTURE (see oracle/__init__.py).  Line-for-line Python restatement of
 
-  /root/reference/src/core/sequence.rs:150-238          Sequence
-  /root/reference/src/core/block_manager.rs:51-299,346-442,552-604,645-697   BlockManager (prefix cache, no swap)
-  /root/reference/src/core/prefix_cache.rs              PrefixCache (hash chain of full blocks, leaf LRU)
-  /root/reference/src/core/scheduler.rs:186-380         add, schedule
-  /root/reference/src/core/scheduler.rs:500-654         postprocess, clear_finished
-  /root/reference/src/core/scheduler.rs:718-785         filter_prefill_finished
-  /root/reference/src/core/runner.rs:952-1388           prepare_block_tables / prefill / decode
+  src/core/sequence.rs:150-238          Sequence
+  src/core/block_manager.rs:51-299,346-442,552-604,645-697   BlockManager (prefix cache, no swap)
+  src/core/prefix_cache.rs              PrefixCache (hash chain of full blocks, leaf LRU)
+  src/core/scheduler.rs:186-380         add, schedule
+  src/core/scheduler.rs:500-654         postprocess, clear_finished
+  src/core/scheduler.rs:718-785         filter_prefill_finished
+  src/core/runner.rs:952-1388           prepare_block_tables / prefill / decode
 
 Written independently of the C++ mirror (vllm_rs_b200/csrc/host/scheduler.cpp) -- plain
 Python containers, same control flow as the Rust -- so that the two can be compared.
@@ -90,7 +90,7 @@ M64 = (1 << 64) - 1
 
 def siphash(data: bytes, k0: int = 0, k1: int = 0, c_rounds: int = 1, d_rounds: int = 3) -> int:
     """SipHash-c-d (Aumasson & Bernstein).  Rust's `DefaultHasher::new()` -- what prefix_cache.rs:337-349
-    hashes with -- is SipHash-1-3 with the all-zero key (std is not part of /root/reference; this is the
+    hashes with -- is SipHash-1-3 with the all-zero key (std is not part of the reference project; this is the
     published algorithm, pinned in tests/ against the paper's SipHash-2-4 vector)."""
     v0 = k0 ^ 0x736F6D6570736575
     v1 = k1 ^ 0x646F72616E646F6D

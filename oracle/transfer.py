@@ -1,11 +1,11 @@
 """PD transfer wire frames, restated (TEST INFRASTRUCTURE, see oracle/__init__.py).
 
-/root/reference/src/transfer/comm.rs:384-410: a frame is a 4-byte little-endian length followed by
+src/transfer/comm.rs:384-410: a frame is a 4-byte little-endian length followed by
 `bincode::serialize(&TransferMessage)`.  bincode is a crates.io dependency (Cargo.toml:37, `bincode = "1.3.1"`),
 not vendored: this restates its published default configuration -- little endian, fixed-width integers, `usize`
 as u64, enum variant index as u32, `Vec<T>` / `String` as a u64 length followed by the elements, tuples and
 structs as their fields in declaration order -- for the messages that carry or release KV bytes
-(/root/reference/src/transfer/mod.rs:82-125):
+(src/transfer/mod.rs:82-125):
 
     enum TransferMessage { TransferPrefill(Sequence) = 0, AvailableTokenResponse(usize) = 1,
                            TransferKvCache(FinishedPrefillData) = 2, ReleaseKvCache(usize) = 3 }
@@ -69,7 +69,7 @@ def parse_kv_remote_frame(buf: bytes):
 
 
 # ---------------------------------------------------------------- engine <-> runner frames of the decode step
-# /root/reference/src/runner/mod.rs:168-295 (MessageType variant order), core/sequence.rs:52-83 (DecodeSequence),
+# src/runner/mod.rs:168-295 (MessageType variant order), core/sequence.rs:52-83 (DecodeSequence),
 # utils/config.rs:504-537 (SamplingParams: stop_token_ids is #[serde(skip)]; grammar travels as Option<String>).
 MT_RUN_DECODE, MT_RUN_RESPONSE, MT_FINISH_DECODE, MT_HEARTBEAT, MT_KV_SWAP, MT_KV_SWAP_RESPONSE = 4, 5, 8, 14, 21, 22
 MT_CLEAR_BLOCKS, MT_CLEAR_BLOCKS_RESPONSE, MT_SHUTDOWN = 31, 32, 34

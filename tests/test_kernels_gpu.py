@@ -198,7 +198,7 @@ def _wna_case(K, N, M, fmt, bits, seed, group=128):
     return qw, qz, s, torch.from_numpy(W), x
 
 
-# flat GEMV / round-1 tcgen05 decode kernel (M <= 64) / general tcgen05 / stream-K tcgen05 decode kernel (M <= 32)
+# flat GEMV / tile-split tcgen05 decode kernel (M <= 64) / general tcgen05 / stream-K tcgen05 decode kernel (M <= 32)
 @pytest.mark.parametrize("variant", [1, 2, 4, 5, 6])
 @pytest.mark.parametrize("fmt,bits,K,N,M", [
     ("awq", 4, 4096, 1024, 1), ("awq", 4, 4096, 6144, 32), ("awq", 4, 14336, 4096, 5),
@@ -268,7 +268,7 @@ def test_wna16_streamk_decode(ops, fmt, bits, K, N, M, group, epi, variant):
     assert torch.equal(y2, y)                                      # contributor-ordered sums: deterministic
     if epi == "none":
         # the exact product x @ ((q - z) * s), no fp16 rounding of the weights: the post-MMA scale must be at least
-        # as close to it as the round-1 kernel, which multiplies with the reference's fp16-rounded weights
+        # as close to it as the tile-split kernel, which multiplies with the reference's fp16-rounded weights
         q = oq.unpack_awq(qw) if fmt == "awq" else oq.unpack_gptq(qw, bits)
         if qz is None:
             z = np.full((K // group, N), 1 << (bits - 1), dtype=np.int32)

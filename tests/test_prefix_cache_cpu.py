@@ -2,7 +2,7 @@
 
 Three layers of evidence:
   * the chain hash: Rust's `DefaultHasher::new()` (prefix_cache.rs:337-349) is SipHash-1-3 with the
-    all-zero key.  `std` is not part of /root/reference, so the oracle restates the published algorithm
+    all-zero key.  `std` is not part of the reference project, so the oracle restates the published algorithm
     and is pinned against (a) the SipHash paper's 2-4 test vector and (b) CPython's own SipHash-1-3
     (`hash(bytes)` under PYTHONHASHSEED=0 uses the zero key) -- an independent implementation;
   * the reference's own unit tests (prefix_cache.rs:362-403) replayed on the oracle's PrefixCache;

@@ -1,5 +1,5 @@
 import sys, os
-sys.path.insert(0, "/root/repo"); sys.path.insert(0, "/root/repo/tests")
+_root = os.path.dirname(os.path.dirname(os.path.abspath(__file__))); sys.path.insert(0, _root); sys.path.insert(0, os.path.join(_root, "tests"))
 import numpy as np, torch
 from oracle import quant as oq, model as om
 from vllm_rs_b200 import ops

@@ -3,8 +3,8 @@
 // key of [0, context_len) is in the cache and is read through the block table).
 //
 // Replaces the prefill branch of attention_rs::PagedAttention::forward
-// (/root/reference/src/models/layers/attention.rs:808-820) with the metadata of
-// ModelRunner::prepare_prefill (/root/reference/src/core/runner.rs:978-1241): cu_seqlens_q u32
+// (src/models/layers/attention.rs:808-820) with the metadata of
+// ModelRunner::prepare_prefill (src/core/runner.rs:978-1241): cu_seqlens_q u32
 // [B+1], context_lens u32 [B] (= num_cached_tokens + chunk tokens), block_tables u32 [B, max_blocks].
 //
 // Design (flash-attention-2 dataflow on mma.sync, K/V pages gathered by TMA like the decode

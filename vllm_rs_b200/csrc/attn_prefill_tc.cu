@@ -1,8 +1,8 @@
 // Varlen causal prefill attention over the paged cache on tcgen05 tensor cores (head_dim 128).
 //
 // Same contract as attn_prefill.cu (the prefill branch of PagedAttention::forward,
-// /root/reference/src/models/layers/attention.rs:808-820, metadata of prepare_prefill,
-// /root/reference/src/core/runner.rs:978-1241) -- that file's mma.sync kernel stays as the head_dim 64
+// src/models/layers/attention.rs:808-820, metadata of prepare_prefill,
+// src/core/runner.rs:978-1241) -- that file's mma.sync kernel stays as the head_dim 64
 // path and as the A/B baseline (B200_PREFILL_ATTN=mma).
 //
 // A CTA owns 128 rows = 128/G query tokens x the G query heads of ONE kv head (row = token * G + head,

@@ -1,8 +1,8 @@
 // Tensor-parallel communicator: one process per GPU, one NCCL communicator, one collective
 // (all-reduce SUM of the row-parallel GEMM output) -- exactly the reference's data plane:
-//   Comm::from_rank(device, rank, num_shards, nccl_id)   /root/reference/src/runner/runner.rs:81-89
-//   Id shipped as 128 raw bytes                           /root/reference/src/runner/mod.rs:33-58
-//   AllReduce::cuda_fwd -> comm.all_reduce(SUM)           /root/reference/src/models/layers/distributed.rs:335-395
+//   Comm::from_rank(device, rank, num_shards, nccl_id)   src/runner/runner.rs:81-89
+//   Id shipped as 128 raw bytes                           src/runner/mod.rs:33-58
+//   AllReduce::cuda_fwd -> comm.all_reduce(SUM)           src/models/layers/distributed.rs:335-395
 // NCCL is resolved with dlopen("libnccl.so.2") so single-GPU users need no NCCL at all.
 //
 // On top of the NCCL baseline there is a one-shot all-reduce for decode-sized messages

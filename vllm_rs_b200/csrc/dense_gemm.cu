@@ -1,7 +1,7 @@
 // Dense fp16 GEMM for the unquantised linears on the path (lm_head; fp16 checkpoints):
 //   C[m, n] = A[m, k] x W[n, k]^T, fp32 accumulate, fp16 or fp32 output.
-// Reference: Linear::forward -> candle -> cuBLAS (/root/reference/src/models/layers/linear.rs:75-123)
-// and the f32 logits cast in /root/reference/src/models/llama.rs:311-320.
+// Reference: Linear::forward -> candle -> cuBLAS (src/models/layers/linear.rs:75-123)
+// and the f32 logits cast in src/models/llama.rs:311-320.
 // Default: the hand-written tcgen05 kernel of dense_gemm_tc.cu.  B200_DENSE=cublas (or mode 0) selects the
 // library GEMM the reference itself calls -- ONLY as an explicit A/B arm: a shape the tcgen05 kernel does not
 // take (K % 64 != 0, N % 8 != 0, unaligned pointers) latches an error, there is no silent library fallback.

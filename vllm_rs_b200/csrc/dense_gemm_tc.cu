@@ -1,12 +1,12 @@
 // Dense fp16 GEMM on tcgen05 (SS mode): C[m, n] = A[m, k] x W[n, k]^T, fp32 accumulation in TMEM,
 // fp16 or fp32 output, optional bias.
 //
-// Replaces the cuBLAS call behind Linear::forward (/root/reference/src/models/layers/linear.rs:75-123)
+// Replaces the cuBLAS call behind Linear::forward (src/models/layers/linear.rs:75-123)
 // for fp16 checkpoints (BASELINE.json configs[2]: Llama-3-8B fp16 chunked prefill), the lm_head
-// (/root/reference/src/models/llama.rs:311-320) and -- together with wna16_dequant_kernel below --
+// (src/models/llama.rs:311-320) and -- together with wna16_dequant_kernel below --
 // the W4A16 / W8A16 linears of large prefill steps, where dequantising a layer's weights ONCE into an
 // fp16 scratch and running this kernel beats re-dequantising them for every 256-token tile
-// (the Marlin call of /root/reference/src/utils/gptq.rs:118-146 at M = thousands of tokens).
+// (the Marlin call of src/utils/gptq.rs:118-146 at M = thousands of tokens).
 //
 // Both operands are K-major, so both arrive through TMA (SWIZZLE_128B, 64-element K blocks) and
 // feed tcgen05.mma.kind::f16 through shared-memory descriptors.  "P" is the operand whose rows

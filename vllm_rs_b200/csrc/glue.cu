@@ -4,13 +4,13 @@
 // kernels: 128-bit loads, fp32 math, one rounding to fp16 on store.
 //
 // Reference call sites they replace:
-//   FusedRope::apply_inplace          /root/reference/src/models/layers/rotary_emb.rs:88-104
-//   cache write in PagedAttention     /root/reference/src/models/layers/attention.rs:808-820
-//   NormX::forward / rms_norm         /root/reference/src/models/layers/others.rs:11-66
-//   residual adds                     /root/reference/src/models/llama.rs:107-131
-//   act(gate) * up                    /root/reference/src/models/layers/mlp.rs:451-469
-//   embedding / index_select          /root/reference/src/models/llama.rs:269-310
-//   logits.argmax                     /root/reference/src/utils/logits_processor.rs:67-70
+//   FusedRope::apply_inplace          src/models/layers/rotary_emb.rs:88-104
+//   cache write in PagedAttention     src/models/layers/attention.rs:808-820
+//   NormX::forward / rms_norm         src/models/layers/others.rs:11-66
+//   residual adds                     src/models/llama.rs:107-131
+//   act(gate) * up                    src/models/layers/mlp.rs:451-469
+//   embedding / index_select          src/models/llama.rs:269-310
+//   logits.argmax                     src/utils/logits_processor.rs:67-70
 #include "../../include/b200_vllm.h"
 #include <cuda_fp8.h>
 #include <cstdlib>

@@ -1,7 +1,7 @@
 // bincode 1.3.1 (default configuration) reader / writer shared by the wire-frame code of the host mirror
 // (runner_wire.cpp, scheduler.cpp): little endian, fixed-width integers, usize / isize as 64 bit, enum variant as
 // u32, Option as one tag byte, Vec / String / HashMap as a u64 length followed by the elements.  SamplingParams
-// follows /root/reference/src/utils/config.rs:504-537 (`stop_token_ids` is #[serde(skip)]).
+// follows src/utils/config.rs:504-537 (`stop_token_ids` is #[serde(skip)]).
 #pragma once
 #include <cstdint>
 #include <cstring>
@@ -11,7 +11,7 @@
 namespace b200 {
 namespace wire {
 
-// variant indices of MessageType, in declaration order (/root/reference/src/runner/mod.rs:168-249)
+// variant indices of MessageType, in declaration order (src/runner/mod.rs:168-249)
 enum : uint32_t {
   kInit = 0, kInitAck = 1, kLoadingProgress = 2, kRunPrefill = 3, kRunDecode = 4, kRunResponse = 5, kRunEmbed = 6,
   kRunResponseEmbed = 7, kFinishDecode = 8, kHeartbeat = 14, kKVCacheSwap = 21, kKVCacheSwapResponse = 22,

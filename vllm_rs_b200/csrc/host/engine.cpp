@@ -1,5 +1,5 @@
 // The engine's decode step as ONE native call: the 3-phase loop of
-//   /root/reference/src/core/engine.rs:1693-1757   (prepare_step -> run_forward -> finish_step)
+//   src/core/engine.rs:1693-1757   (prepare_step -> run_forward -> finish_step)
 // for a decode batch: Scheduler::schedule (scheduler.rs:200-380), ModelRunner::prepare_decode
 // (core/runner.rs:1243-1388) into pinned staging owned by this handle, ModelRunner::run
 // (b200_runner_decode_host: H2D, CUDA-graph replay, D2H, stream sync), Scheduler::postprocess and

@@ -2,13 +2,13 @@
 // TP rank), optionally captured into CUDA graphs per batch bucket.
 //
 // C++ mirror of the decode branch of ModelRunner::run
-//   /root/reference/src/core/runner.rs:743-896   (prepare -> forward -> sample)
+//   src/core/runner.rs:743-896   (prepare -> forward -> sample)
 // over LLaMaForCausalLM::forward_inner / LLaMaDecoderLayer::forward
-//   /root/reference/src/models/llama.rs:107-131,269-321
-// Attention::forward_ext  /root/reference/src/models/layers/attention.rs:648-839
-// MLP::forward            /root/reference/src/models/layers/mlp.rs:451-469
-// TensorParallelRowLinear /root/reference/src/models/layers/distributed.rs:438-454
-// GraphCapturer           /root/reference/src/utils/graph.rs:370-377,448-835
+//   src/models/llama.rs:107-131,269-321
+// Attention::forward_ext  src/models/layers/attention.rs:648-839
+// MLP::forward            src/models/layers/mlp.rs:451-469
+// TensorParallelRowLinear src/models/layers/distributed.rs:438-454
+// GraphCapturer           src/utils/graph.rs:370-377,448-835
 //
 // Launch plan per layer (5 kernels + 2 small ones, vs 17-22 in the reference):
 //   [add+]rmsnorm -> fused qkv W4A16 GEMM (+bias) -> RoPE + KV write -> paged attention

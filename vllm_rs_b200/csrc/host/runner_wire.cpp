@@ -1,11 +1,11 @@
 // Engine <-> runner-process wire format of the decode step.
 //
-// Mirrors /root/reference/src/runner/mod.rs:168-295 (`MessageType`, `send_local` / `receive_local`: a frame is a
+// Mirrors src/runner/mod.rs:168-295 (`MessageType`, `send_local` / `receive_local`: a frame is a
 // u32 little-endian length followed by `bincode::serialize(&MessageType)`; the receiver answers every frame with ONE
-// acknowledgment byte 0x01), /root/reference/src/core/sequence.rs:52-83 (`DecodeSequence`),
-// /root/reference/src/utils/config.rs:504-537 (`SamplingParams`; `stop_token_ids` is `#[serde(skip)]`, `grammar` goes
+// acknowledgment byte 0x01), src/core/sequence.rs:52-83 (`DecodeSequence`),
+// src/utils/config.rs:504-537 (`SamplingParams`; `stop_token_ids` is `#[serde(skip)]`, `grammar` goes
 // over bincode as `Option<String>` of its JSON, config.rs:128-145) and the decode metadata a runner derives from such
-// a message (/root/reference/src/core/runner.rs:1243-1264).  bincode 1.3.1 defaults (Cargo.toml:37): little endian,
+// a message (src/core/runner.rs:1243-1264).  bincode 1.3.1 defaults (Cargo.toml:37): little endian,
 // fixed-width integers, usize / isize as 64 bit, enum variant as u32, Option as one tag byte, Vec / String / HashMap
 // as a u64 length followed by the elements.
 //

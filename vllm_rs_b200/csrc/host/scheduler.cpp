@@ -1,14 +1,14 @@
 // Host-side integer state of the hot path: Sequence, BlockManager, Scheduler and the
 // per-step input preparation.  C++ mirror of
-//   /root/reference/src/core/sequence.rs           (Sequence, num_blocks, last_block_num_tokens)
-//   /root/reference/src/core/block_manager.rs:51-299 (FIFO free list, allocate_fresh,
+//   src/core/sequence.rs           (Sequence, num_blocks, last_block_num_tokens)
+//   src/core/block_manager.rs:51-299 (FIFO free list, allocate_fresh,
 //        may_append, can_append, deallocate in reverse table order)
-//   /root/reference/src/core/scheduler.rs:186-380,500-654,718-785
+//   src/core/scheduler.rs:186-380,500-654,718-785
 //        (add, schedule, postprocess, clear_finished, filter_prefill_finished)
-//   /root/reference/src/core/runner.rs:952-1388 (prepare_block_tables / prefill / decode)
+//   src/core/runner.rs:952-1388 (prepare_block_tables / prefill / decode)
 // Block ids, block tables, slot mappings, context lens and cu_seqlens must be BIT-EXACT
 // with the reference; tests/ compare this file against oracle/ on scripted traces.
-//   /root/reference/src/core/prefix_cache.rs (hash chain of full blocks + leaf LRU) and
+//   src/core/prefix_cache.rs (hash chain of full blocks + leaf LRU) and
 //   block_manager.rs:179-221,275-299,346-442,552-604,657-672 (allocate_with_prefix, cache_sequence,
 //        reference-counted sharing, eviction); scheduler.rs:288-337,1167-1175 (eviction under pressure)
 //   CPU swap of running sequences (block_manager.rs:255-272,878-1000; scheduler.rs:303-337,830-954): the
@@ -1178,7 +1178,7 @@ int32_t b200_scheduler_load_sequence(b200_scheduler* s, const uint8_t* frame, in
 }
 
 // KVCacheAllocator::plan_allocation for dense models
-//   /root/reference/src/utils/kvcache_allocator.rs:126-141 (kv heads per shard), 447-468
+//   src/utils/kvcache_allocator.rs:126-141 (kv heads per shard), 447-468
 //   (per_block_bytes), 553-612 (auto_decide_params), 616-707 (plan_allocation)
 // ---- recurrent-state slots and host-driven (streamed) sequences
 int32_t b200_scheduler_enable_state_slots(b200_scheduler* s, int32_t n) {

@@ -1,6 +1,6 @@
 // PD (prefill / decode) KV-cache hand-off: the wire frames and the block movement around them.
 //
-// Mirrors /root/reference/src/transfer/mod.rs:82-125 (KVTransferHandle, FinishedPrefillData, TransferMessage),
+// Mirrors src/transfer/mod.rs:82-125 (KVTransferHandle, FinishedPrefillData, TransferMessage),
 // transfer/comm.rs:384-410 (frame = u32 LE length + bincode 1.3.1 body: little endian, fixed-width integers,
 // usize as u64, enum variant as u32, Vec length as u64 -- Cargo.toml:37) and the two data legs of
 // transfer/mod.rs:260-311,370-470: RemoteTcp (server: cache blocks -> contiguous bytes per layer, client: bytes ->

@@ -1,8 +1,8 @@
 // Paged-KV attention, decode step (one query token per sequence).
 //
 // Replaces the decode branch of attention_rs::PagedAttention::forward as called from
-// /root/reference/src/models/layers/attention.rs:808-820 with the metadata built by
-// ModelRunner::prepare_decode (/root/reference/src/core/runner.rs:1243-1388):
+// src/models/layers/attention.rs:808-820 with the metadata built by
+// ModelRunner::prepare_decode (src/core/runner.rs:1243-1388):
 //   block_tables u32 [B, max_blocks] (zero padded), context_lens u32 [B] -- both read
 //   on the device so the launch is CUDA-graph safe (graph.rs:741-767 pads rows with
 //   context_len 0).

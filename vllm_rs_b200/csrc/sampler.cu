@@ -3,7 +3,7 @@
 // seeded step-seed stream.
 //
 // Replaces attention_rs::sampler::Sampler::sample_cuda as called from
-//   LogitsProcessor::sample_with_strategy  /root/reference/src/utils/logits_processor.rs:199-231
+//   LogitsProcessor::sample_with_strategy  src/utils/logits_processor.rs:199-231
 // (k, p, t mapping of :208-216) with the semantics of the source-visible CPU branch
 //   sample_topk_topp / sample_topk / sample_topp  logits_processor.rs:84-196
 // i.e. probabilities are the FULL-vocabulary softmax, the top-p cut walks the un-renormalised top-k

@@ -2,7 +2,7 @@
 // decoding for AWQ / GPTQ checkpoints and register dequantisation to fp16.
 //
 // Quantised formats follow what the reference loader implies
-// (/root/reference/src/models/layers/wna16.rs:56-83,127-152):
+// (src/models/layers/wna16.rs:56-83,127-152):
 //   GPTQ  qweight i32 [K/pack, N], element (k,n) = (w[k/pack][n] >> bits*(k%pack)) & mask
 //         qzeros  i32 [K/G, N/pack], zero = field(n%pack) + 1, scales f16 [K/G, N]
 //   AWQ   qweight i32 [K, N/8], nibble j of a word holds output 8c + {0,2,4,6,1,3,5,7}[j]

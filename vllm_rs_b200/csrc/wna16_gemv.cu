@@ -3,7 +3,7 @@
 //
 // Replaces attention_rs::kernels::ffi::{awq_repack, gptq_repack} and the small-M side of
 // {marlin_awq_4bit_f16, marlin_4bit_f16, gemm_half_q_half_alt} as called from
-// /root/reference/src/utils/gptq.rs:100-200,314-333.
+// src/utils/gptq.rs:100-200,314-333.
 //
 // GEMV design: thread = one output channel, CTA = one 128-channel weight tile x a K split.
 // A warp's 32 threads read 512 contiguous bytes of packed weights per step (16 B each =
@@ -305,7 +305,7 @@ void b200_wna16_gemm_ex(const void* a, const void* b_packed, const void* scales,
   }
   if (variant == 2 || variant == 3 || variant == 4 || (variant == 0 && m > gemv_max_m())) {
     if (variant == 0 && launch_wna16_sk(p, st)) return;        // persistent stream-K decode kernel (M <= 32)
-    if (variant != 4 && launch_wna16_tc_dec(p, st)) return;    // round-1 decode kernel (M <= 64; A/B arm: variant 2)
+    if (variant != 4 && launch_wna16_tc_dec(p, st)) return;    // tile-split decode kernel (M <= 64; A/B arm: variant 2)
     if (launch_wna16_tc(p, st)) return;
     if (variant >= 2) { set_error(1, "wna16: shape unsupported by the tcgen05 variant"); return; }
   }

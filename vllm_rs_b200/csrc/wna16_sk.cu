@@ -1,14 +1,14 @@
 // W4A16 / W8A16 GEMM on tcgen05 for DECODE batches (M <= 32): persistent stream-K variant.
 //
-// Replaces marlin_*_4bit_f16 / gemm_half_q_half_alt for decode shapes (/root/reference/src/utils/gptq.rs:118-195,
+// Replaces marlin_*_4bit_f16 / gemm_half_q_half_alt for decode shapes (src/utils/gptq.rs:118-195,
 // wna16.rs:263-306).  Same data layout, epilogues and split meeting point as wna16_tc_dec.cu; what changes is how
-// the work is cut and who does what.  Motivation (round-2 measurements of the round-1 kernel,
+// the work is cut and who does what.  Motivation (measurements of the tile-split decode kernel,
 // profiles/r2_b_dec_gemm_diet_experiments.txt): two thirds of its issued
 // instructions are pipeline bookkeeping, gate|up runs 1.51 waves, ~4 us of serial epilogue per launch.
 // Outcome (profiles/r2_j_sk_vs_dec.txt, ten measured iterations): bit-reproducible, the SAME weight arithmetic as
-// the reference and the round-1 kernel (w = fp16((q - z) * s), one rounding, before the MMA), parity green on every
+// the reference and the tile-split kernel (w = fp16((q - z) * s), one rounding, before the MMA), parity green on every
 // shape / epilogue at kernel level and through the whole runner with every decode GEMM forced onto it
-// (tests/test_runner_gpu.py::test_runner_parity_with_the_streamk_gemm_forced).  FASTER than the round-1 kernel on
+// (tests/test_runner_gpu.py::test_runner_parity_with_the_streamk_gemm_forced).  FASTER than the tile-split kernel on
 // big-N projections in isolation (gate|up: 25.6 vs 30.0 us at one token, 31.2 vs 32.4 us at 32), slower on the
 // small-N ones (whole layer at 32 tokens 68.4 vs 65.7 us); in the decode step it wins up to 16 tokens -- the
 // automatic dispatch uses it there (sk_mode below).
@@ -18,7 +18,7 @@
 //     streams bytes [b*share, (b+1)*share) * unit_bytes: no wave tail, every SM busy on every shape.
 //     A tile cut by a CTA boundary is finished by the split meeting point (per-CTA partial slots, arrival
 //     counter, last arriver reduces in contributor order: deterministic).  Small-N projections are cut into the
-//     same <= 4 aligned pieces per tile as the round-1 kernel, so a finaliser sums at most four partial tiles.
+//     same <= 4 aligned pieces per tile as the tile-split kernel, so a finaliser sums at most four partial tiles.
 //   * three dequant groups (4 warps = 128 channels each) take the units round robin; a group dequantises a unit
 //     in registers (zero point and scale of the unit read from global memory three units ahead: no staging ring),
 //     tcgen05.st's the fp16 weights to TMEM, and its own issuer warp runs the eight tcgen05.mma of the unit into
@@ -802,7 +802,7 @@ wna16_sk_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
         }
         const uint32_t z = has_z ? ((zq[0] >> zshift) & zmask) + zadd : (1u << (BITS - 1));
         // the constants of make_dq (wna16.cuh) as bit patterns: 1024 + z, 64 + z, (s, s) -- the SAME arithmetic as
-        // the round-1 kernel and the reference: w = fp16((q - z) * s), one rounding
+        // the tile-split kernel and the reference: w = fp16((q - z) * s), one rounding
         DqConst dq;
         dq.s2 = u32_as_h2(sq[0] * 0x00010001u);
         dq.zlo = u32_as_h2((0x6400u | z) * 0x00010001u);
@@ -912,12 +912,12 @@ wna16_sk_kernel(const __grid_constant__ CUtensorMap xmap, const Args a) {
 }
 
 // B200_DEC_SK: 0 = never, 1 = every shape the kernel takes (M <= 32), 2 (default) = where it measured faster than the
-// round-1 kernel on B200 IN THE DECODE STEP (profiles/r2_ai_sk_policy_ab.txt, same-box A/B): at most 16 tokens on
+// tile-split kernel on B200 IN THE DECODE STEP (profiles/r2_ai_sk_policy_ab.txt, same-box A/B): at most 16 tokens on
 // projections with at least 32 units per CTA (gate|up): b=1 2.55 -> 2.44 ms per step.  At 32 tokens the kernel is
 // faster in isolation (gate|up 31.2 vs 32.4 us) but the step gets SLOWER (5.05 -> 5.20 ms): a persistent grid ends on
-// all SMs at once, while the round-1 kernel's half-empty second wave lets the next GEMM's CTAs start streaming their
+// all SMs at once, while the tile-split kernel's half-empty second wave lets the next GEMM's CTAs start streaming their
 // weights early under programmatic dependent launch.  The small-N projections (qkv, o, down: 10-25 units per CTA)
-// stay on the round-1 kernel at every batch: 12.4 / 8.7 / 16.2 vs 9.6 / 8.2 / 15.4 us at 32 tokens.
+// stay on the tile-split kernel at every batch: 12.4 / 8.7 / 16.2 vs 9.6 / 8.2 / 15.4 us at 32 tokens.
 static int sk_mode() {
   static int v = -1;
   if (v < 0) {
@@ -933,11 +933,11 @@ static bool launch_epi(const WnaParams& p, cudaStream_t st) {
   const int KC = p.K / kChunkK, KP = p.K / kUnitK;
   const int tiles = p.N / kTileN;
   const long units = static_cast<long>(tiles) * KP;
-  // one CTA per SM; never less than two units (four chunks) per CTA, as in the round-1 split rule
+  // one CTA per SM; never less than two units (four chunks) per CTA, as in the tile-split kernel's split rule
   long G = sm_count();
   if (G > units / 2) G = units / 2 > 0 ? units / 2 : 1;
   int share = static_cast<int>((units + G - 1) / G);
-  // Small-N projections (qkv, o, down): cut every tile into the SAME s <= 4 aligned pieces (s | KP), as the round-1
+  // Small-N projections (qkv, o, down): cut every tile into the SAME s <= 4 aligned pieces (s | KP), as the tile-split
   // kernel does -- the last arriver then sums at most four partial tiles, one load batch of the finaliser; a free-
   // running share cut `o` into six and `down` into five or six.  Big-N projections keep the pure stream-K share.
   if (static_cast<long>(tiles) * 4 <= sm_count() + sm_count() / 8) {

@@ -1,7 +1,7 @@
 // W4A16 / W8A16 GEMM on tcgen05 tensor cores with register dequant feeding TMEM.
 //
 // Replaces marlin_awq_4bit_f16 / marlin_4bit_f16 / gemm_half_q_half_alt
-// (/root/reference/src/utils/gptq.rs:118-195) for every M > 4 (decode batches and prefill).
+// (src/utils/gptq.rs:118-195) for every M > 4 (decode batches and prefill).
 //
 // "Swap-AB" formulation: D^T[n, m] = sum_k W^T[n, k] * X[m, k].  The WEIGHT tile is the MMA
 // A operand (M_mma = 128 output channels = 128 TMEM lanes), the activations are the B operand

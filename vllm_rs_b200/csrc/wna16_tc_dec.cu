@@ -52,7 +52,7 @@ __device__ uint32_t* g_dec_trace = nullptr;
 #endif
 #ifndef B200_DEC_UNROLL
 #define B200_DEC_UNROLL 0         // 1 = ring-unrolled dequant loop: -5 % in tools/gemm_bench.py, nothing in the decode
-#endif                            // step (cold instruction fetch of a 50 % larger kernel): the round-1 loop stays the default
+#endif                            // step (cold instruction fetch of a 50 % larger kernel): the rolled loop stays the default
 #ifndef B200_DEC_SXS
 #define B200_DEC_SXS 3            // activation super-stages
 #endif
@@ -329,7 +329,7 @@ wna16_tc_dec_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     };
 #if B200_DEC_UNROLL
     {
-      // Ring-unrolled form of the loop below (round 2).  The ncu stall counters say the loop is bound by its serial
+      // Ring-unrolled form of the loop below.  The ncu stall counters say the loop is bound by its serial
       // bookkeeping, not by the dequant arithmetic (removing 60 % of the arithmetic bought 10 %): ring-stage indices,
       // barrier addresses, phase bits and TMEM columns recomputed per chunk with dependent ISETP / SEL / IMAD chains.
       // Unrolling by P = lcm(weight stages, A stages) chunks makes every one of them a compile-time constant of the

@@ -49,14 +49,15 @@ def build(cfg, tensors, *, dtype=torch.bfloat16, device="cuda", num_blocks, max_
                      latent_norm_w=vec(p + "dkv.norm"), sink=vec(p + "sink") if p + "sink" in tensors else None)
         elif kind == "delta":
             mixer = MIXER_DELTA_RULE
-            d.update(heads=m["heads"], kv_heads=m["kv_heads"], dim=m["dim"], vdim=m["vdim"], conv_taps=m["conv"])
+            d.update(heads=m["heads"], kv_heads=m.get("kv_heads", m["heads"]), dim=m["dim"], vdim=m["vdim"],
+                     conv_taps=m["conv"])
             t.update(w_in=mat(p + "q", p + "k", p + "v", p + "b", p + "a", p + "g"), w_o=mat(p + "o"),
                      conv_w=vec(p + "q.conv", p + "k.conv", p + "v.conv"), a_log=vec(p + "A_log"),
                      dt_bias=vec(p + "dt_bias"), out_norm_w=vec(p + "norm"))
         elif kind == "mamba2":
             mixer = MIXER_SSD
-            d.update(heads=m["heads"], kv_heads=m["groups"], vdim=m["vdim"], state=m["state"], conv_taps=m["conv"],
-                     norm_groups=m["norm_groups"])
+            d.update(heads=m["heads"], kv_heads=m.get("groups", 1), vdim=m["vdim"], state=m["state"],
+                     conv_taps=m["conv"], norm_groups=m.get("norm_groups", 1))
             t.update(w_in=mat(p + "in"), w_o=mat(p + "o"), conv_w=vec(p + "conv"), conv_b=vec(p + "conv.b"),
                      a_log=vec(p + "A_log"), dt_bias=vec(p + "dt_bias"), d_skip=vec(p + "D"), out_norm_w=vec(p + "norm"))
         else:

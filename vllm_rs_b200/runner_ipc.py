@@ -1,5 +1,5 @@
 """Engine <-> runner-process protocol of a step, over any stream socket (harness mirror of
-/root/reference/src/runner/mod.rs:248-295 `send_local` / `receive_local`, and of the runner binary's message loop,
+src/runner/mod.rs:248-295 `send_local` / `receive_local`, and of the runner binary's message loop,
 runner/runner.rs:249-434, for the messages of the hot path).
 
 A message is one frame (u32 little-endian length + bincode 1.3.1 body); the receiver answers every frame with ONE

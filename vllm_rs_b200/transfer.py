@@ -1,5 +1,5 @@
 """PD (prefill / decode) KV hand-off over the C ABI: mirrors the data side of
-/root/reference/src/transfer/mod.rs (Transfer::transfer_kv_cache / Transfer::receive_kv_cache) -- same names and
+src/transfer/mod.rs (Transfer::transfer_kv_cache / Transfer::receive_kv_cache) -- same names and
 argument meaning -- on top of b200_pd_* (csrc/host/transfer.cpp).  Sockets and the listener thread are the host's."""
 from __future__ import annotations
 
