@@ -14,7 +14,8 @@
 //                     y = S^T C + D x.  state [slots, heads, nstate, vdim].
 // In both scans eight lanes share one column of S (one value channel), each holding every eighth row in registers,
 // and walk the sequence's tokens in order: the exact recurrence, no chunked reformulation, so a portion boundary
-// cannot change the arithmetic.
+// cannot change the arithmetic.  The tokens' inputs are staged in shared memory a pass at a time through two buffers
+// filled by cp.async, so the walk never waits for global memory.
 #include "../../include/b200_vllm.h"
 #include "seqmix.cuh"
 
@@ -86,9 +87,20 @@ __global__ void short_conv_state_kernel(const float* __restrict__ x, int ldx, fl
   for (int j = 0; j < P; ++j) sp[static_cast<size_t>(j) * C] = keep[j];
 }
 
-// tokens staged in shared memory per pass (static shared memory stays under 48 KB for the widest state)
-constexpr int chunk_for(int rows) { return rows > 128 ? 16 : 32; }
+// tokens staged in shared memory per pass; there are two such buffers (static shared memory stays under 48 KB for
+// the widest state): the next pass's rows arrive by cp.async while the current pass's tokens are walked
+constexpr int chunk_for(int rows) { return rows > 128 ? 8 : rows > 64 ? 16 : 32; }
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
+               "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 constexpr int kRowSplit = 8;       // lanes that share one column of S (each holds every 8th row)
+constexpr int kScanThreads = 128, kScanCols = kScanThreads / kRowSplit;      // columns of S per block
 
 // grid = (column blocks, heads, sequences); block = 128 threads = 16 columns x kRowSplit lanes.  DK = compile-time
 // bound of `dim`; a lane holds the rows i = j * kRowSplit + part of its column.
@@ -101,7 +113,7 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
                   const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx, int heads, int kv_heads, int dim,
                   int vdim) {
   constexpr int RS = kRowSplit, NR = DK / RS, kChunk = chunk_for(DK);
-  __shared__ float ks[kChunk][DK], qs[kChunk][DK], gs[kChunk], bs[kChunk];
+  __shared__ float ks[2][kChunk][DK], qs[2][kChunk][DK], vs[2][kChunk][kScanCols], gs[2][kChunk], bs[2][kChunk];
   const int h = blockIdx.y, b = blockIdx.z;
   const int part = threadIdx.x % RS;
   const int col = blockIdx.x * (blockDim.x / RS) + threadIdx.x / RS;
@@ -119,58 +131,84 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
   }
   const float neg_a = -expf(a_log[h]), dtb = dt_bias[h], qscale = rsqrtf(static_cast<float>(dim));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int c0 = t0; c0 < t1; c0 += kChunk) {
+  for (int e = threadIdx.x; e < 2 * kChunk * DK; e += kScanThreads)       // the padding past `dim` stays zero
+    (&ks[0][0][0])[e] = (&qs[0][0][0])[e] = 0.f;
+  for (int e = threadIdx.x; e < 2 * kChunk * kScanCols; e += kScanThreads) (&vs[0][0][0])[e] = 0.f;
+  __syncthreads();
+  // raw rows of one pass -> buffer `buf` (asynchronous; committed as one group)
+  auto fetch = [&](int c0, int buf) {
     const int n = min(kChunk, t1 - c0);
+    for (int e = threadIdx.x; e < n * dim; e += kScanThreads) {
+      const int r = e / dim, i = e - r * dim;
+      cp_async4(&ks[buf][r][i], k + static_cast<size_t>(c0 + r) * ld + hk * dim + i);
+      cp_async4(&qs[buf][r][i], q + static_cast<size_t>(c0 + r) * ld + hk * dim + i);
+    }
+    for (int e = threadIdx.x; e < n * kScanCols; e += kScanThreads) {
+      const int r = e / kScanCols, c = blockIdx.x * kScanCols + e % kScanCols;
+      if (c < vdim) cp_async4(&vs[buf][r][e % kScanCols], v + static_cast<size_t>(c0 + r) * ld + h * vdim + c);
+    }
+    if (threadIdx.x < n) {
+      cp_async4(&bs[buf][threadIdx.x], b_raw + static_cast<size_t>(c0 + threadIdx.x) * ld_ba + h);
+      cp_async4(&gs[buf][threadIdx.x], a_raw + static_cast<size_t>(c0 + threadIdx.x) * ld_ba + h);
+    }
+    cp_async_commit();
+  };
+  fetch(t0, 0);
+  int buf = 0;
+  for (int c0 = t0; c0 < t1; c0 += kChunk, buf ^= 1) {
+    const int n = min(kChunk, t1 - c0);
+    if (c0 + kChunk < t1) {
+      fetch(c0 + kChunk, buf ^ 1);         // the other buffer's tokens were walked before the last barrier
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
     __syncthreads();
-    // stage and unit-normalise q, k of the chunk: one warp per token row
+    // unit-normalise q, k of the pass in place: one warp per token row
     for (int r = warp; r < n; r += nw) {
-      const float* kr = k + static_cast<size_t>(c0 + r) * ld + hk * dim;
-      const float* qr = q + static_cast<size_t>(c0 + r) * ld + hk * dim;
       float sk = 0.f, sq = 0.f;
       for (int i = lane; i < dim; i += 32) {
-        sk += kr[i] * kr[i];
-        sq += qr[i] * qr[i];
+        sk += ks[buf][r][i] * ks[buf][r][i];
+        sq += qs[buf][r][i] * qs[buf][r][i];
       }
       sk = lanes_sum(sk);
       sq = lanes_sum(sq);
       const float ik = 1.f / sqrtf(sk + 1e-6f), iq = qscale / sqrtf(sq + 1e-6f);
-      for (int i = lane; i < DK; i += 32) {
-        ks[r][i] = i < dim ? kr[i] * ik : 0.f;
-        qs[r][i] = i < dim ? qr[i] * iq : 0.f;
+      for (int i = lane; i < dim; i += 32) {
+        ks[buf][r][i] *= ik;
+        qs[buf][r][i] *= iq;
       }
       if (lane == 0) {
-        bs[r] = sigmoid_f(b_raw[static_cast<size_t>(c0 + r) * ld_ba + h]);
-        gs[r] = expf(neg_a * softplus_f(a_raw[static_cast<size_t>(c0 + r) * ld_ba + h] + dtb));
+        bs[buf][r] = sigmoid_f(bs[buf][r]);
+        gs[buf][r] = expf(neg_a * softplus_f(gs[buf][r] + dtb));
       }
     }
     __syncthreads();
-    float vnext = live ? v[static_cast<size_t>(c0) * ld + h * vdim + col] : 0.f;
     for (int r = 0; r < n; ++r) {          // every lane runs the shuffles; dead columns carry zeros
-      const float vv = vnext;              // the next token's value is fetched under this token's arithmetic
-      if (r + 1 < n && live) vnext = v[static_cast<size_t>(c0 + r + 1) * ld + h * vdim + col];
-      const float g = gs[r];
+      const float vv = vs[buf][r][threadIdx.x / RS];
+      const float g = gs[buf][r];
       float d0 = 0.f, d1 = 0.f;
 #pragma unroll
       for (int j = 0; j < NR; j += 2) {
         s[j] *= g;
-        d0 += ks[r][j * RS + part] * s[j];
+        d0 += ks[buf][r][j * RS + part] * s[j];
         if (j + 1 < NR) {
           s[j + 1] *= g;
-          d1 += ks[r][(j + 1) * RS + part] * s[j + 1];
+          d1 += ks[buf][r][(j + 1) * RS + part] * s[j + 1];
         }
       }
       float dot = d0 + d1;
 #pragma unroll
       for (int o = 1; o < RS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = bs[r] * (vv - dot);
+      const float u = bs[buf][r] * (vv - dot);
       float o0 = 0.f, o1 = 0.f;
 #pragma unroll
       for (int j = 0; j < NR; j += 2) {
-        s[j] += ks[r][j * RS + part] * u;
-        o0 += qs[r][j * RS + part] * s[j];
+        s[j] += ks[buf][r][j * RS + part] * u;
+        o0 += qs[buf][r][j * RS + part] * s[j];
         if (j + 1 < NR) {
-          s[j + 1] += ks[r][(j + 1) * RS + part] * u;
-          o1 += qs[r][(j + 1) * RS + part] * s[j + 1];
+          s[j + 1] += ks[buf][r][(j + 1) * RS + part] * u;
+          o1 += qs[buf][r][(j + 1) * RS + part] * s[j + 1];
         }
       }
       float o = o0 + o1;
@@ -178,6 +216,7 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
       for (int x = 1; x < RS; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
       if (live && part == 0) out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = o;
     }
+    __syncthreads();                       // this buffer is refilled by the next pass's fetch
   }
   if (live) {
 #pragma unroll
@@ -196,7 +235,7 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
                 float* __restrict__ state, const int32_t* __restrict__ slots, const uint32_t* __restrict__ cu,
                 const uint32_t* __restrict__ ctx, int heads, int groups, int nstate, int vdim) {
   constexpr int RS = kRowSplit, NR = NS / RS, kChunk = chunk_for(NS);
-  __shared__ float Bs[kChunk][NS], Cs[kChunk][NS], dts[kChunk], das[kChunk];
+  __shared__ float Bs[2][kChunk][NS], Cs[2][kChunk][NS], xs[2][kChunk][kScanCols], dts[2][kChunk], das[2][kChunk];
   const int h = blockIdx.y, b = blockIdx.z;
   const int part = threadIdx.x % RS;
   const int col = blockIdx.x * (blockDim.x / RS) + threadIdx.x / RS;
@@ -213,33 +252,53 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
     s[j] = (!fresh && live && i < nstate) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
   }
   const float neg_a = -expf(a_log[h]), dtb = dt_bias[h], dsk = d_skip ? d_skip[h] : 0.f;
-  for (int c0 = t0; c0 < t1; c0 += kChunk) {
+  for (int e = threadIdx.x; e < 2 * kChunk * NS; e += kScanThreads)       // the padding past `nstate` stays zero
+    (&Bs[0][0][0])[e] = (&Cs[0][0][0])[e] = 0.f;
+  for (int e = threadIdx.x; e < 2 * kChunk * kScanCols; e += kScanThreads) (&xs[0][0][0])[e] = 0.f;
+  __syncthreads();
+  // raw rows of one pass -> buffer `buf` (asynchronous; committed as one group)
+  auto fetch = [&](int c0, int buf) {
     const int n = min(kChunk, t1 - c0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < n * NS; e += blockDim.x) {
-      const int r = e / NS, i = e % NS;
-      Bs[r][i] = i < nstate ? Bm[static_cast<size_t>(c0 + r) * ld + g * nstate + i] : 0.f;
-      Cs[r][i] = i < nstate ? Cm[static_cast<size_t>(c0 + r) * ld + g * nstate + i] : 0.f;
+    for (int e = threadIdx.x; e < n * nstate; e += kScanThreads) {
+      const int r = e / nstate, i = e - r * nstate;
+      cp_async4(&Bs[buf][r][i], Bm + static_cast<size_t>(c0 + r) * ld + g * nstate + i);
+      cp_async4(&Cs[buf][r][i], Cm + static_cast<size_t>(c0 + r) * ld + g * nstate + i);
     }
+    for (int e = threadIdx.x; e < n * kScanCols; e += kScanThreads) {
+      const int r = e / kScanCols, c = blockIdx.x * kScanCols + e % kScanCols;
+      if (c < vdim) cp_async4(&xs[buf][r][e % kScanCols], x + static_cast<size_t>(c0 + r) * ld + h * vdim + c);
+    }
+    if (threadIdx.x < n) cp_async4(&dts[buf][threadIdx.x], dt_raw + static_cast<size_t>(c0 + threadIdx.x) * ld_dt + h);
+    cp_async_commit();
+  };
+  fetch(t0, 0);
+  int buf = 0;
+  for (int c0 = t0; c0 < t1; c0 += kChunk, buf ^= 1) {
+    const int n = min(kChunk, t1 - c0);
+    if (c0 + kChunk < t1) {
+      fetch(c0 + kChunk, buf ^ 1);         // the other buffer's tokens were walked before the last barrier
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
     if (threadIdx.x < n) {
-      const float dt = softplus_f(dt_raw[static_cast<size_t>(c0 + threadIdx.x) * ld_dt + h] + dtb);
-      dts[threadIdx.x] = dt;
-      das[threadIdx.x] = expf(neg_a * dt);
+      const float dt = softplus_f(dts[buf][threadIdx.x] + dtb);
+      dts[buf][threadIdx.x] = dt;
+      das[buf][threadIdx.x] = expf(neg_a * dt);
     }
     __syncthreads();
-    float xnext = live ? x[static_cast<size_t>(c0) * ld + h * vdim + col] : 0.f;
     for (int r = 0; r < n; ++r) {
-      const float xv = xnext;              // the next token's input is fetched under this token's arithmetic
-      if (r + 1 < n && live) xnext = x[static_cast<size_t>(c0 + r + 1) * ld + h * vdim + col];
-      const float a = das[r], dx = dts[r] * xv;
+      const float xv = xs[buf][r][threadIdx.x / RS];
+      const float a = das[buf][r], dx = dts[buf][r] * xv;
       float y0 = 0.f, y1 = 0.f;
 #pragma unroll
       for (int j = 0; j < NR; j += 2) {
-        s[j] = a * s[j] + dx * Bs[r][j * RS + part];
-        y0 += Cs[r][j * RS + part] * s[j];
+        s[j] = a * s[j] + dx * Bs[buf][r][j * RS + part];
+        y0 += Cs[buf][r][j * RS + part] * s[j];
         if (j + 1 < NR) {
-          s[j + 1] = a * s[j + 1] + dx * Bs[r][(j + 1) * RS + part];
-          y1 += Cs[r][(j + 1) * RS + part] * s[j + 1];
+          s[j + 1] = a * s[j + 1] + dx * Bs[buf][r][(j + 1) * RS + part];
+          y1 += Cs[buf][r][(j + 1) * RS + part] * s[j + 1];
         }
       }
       float y = y0 + y1;
@@ -247,6 +306,7 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
       for (int o = 1; o < RS; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
       if (live && part == 0) out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = y + dsk * xv;
     }
+    __syncthreads();                       // this buffer is refilled by the next pass's fetch
   }
   if (live) {
 #pragma unroll
@@ -282,8 +342,6 @@ void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const 
 #undef B200_CONV
   B200_CUDA_LAUNCH_CHECK();
 }
-
-constexpr int kScanThreads = 128, kScanCols = kScanThreads / kRowSplit;      // columns of S per block
 
 void launch_delta_rule(float* out, const float* q, const float* k, const float* v, int ld, const float* b_raw,
                        const float* a_raw, int ld_ba, const float* a_log, const float* dt_bias, float* state,
