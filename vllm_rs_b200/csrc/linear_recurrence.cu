@@ -131,8 +131,8 @@ delta_rule_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
   }
   const float neg_a = -expf(a_log[h]), dtb = dt_bias[h], qscale = rsqrtf(static_cast<float>(dim));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int e = threadIdx.x; e < 2 * kChunk * DK; e += kScanThreads)       // the padding past `dim` stays zero
-    (&ks[0][0][0])[e] = (&qs[0][0][0])[e] = 0.f;
+  if (dim < DK)                                                           // the padding past `dim` stays zero
+    for (int e = threadIdx.x; e < 2 * kChunk * DK; e += kScanThreads) (&ks[0][0][0])[e] = (&qs[0][0][0])[e] = 0.f;
   for (int e = threadIdx.x; e < 2 * kChunk * kScanCols; e += kScanThreads) (&vs[0][0][0])[e] = 0.f;
   __syncthreads();
   // raw rows of one pass -> buffer `buf` (asynchronous; committed as one group)
@@ -252,8 +252,8 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
     s[j] = (!fresh && live && i < nstate) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
   }
   const float neg_a = -expf(a_log[h]), dtb = dt_bias[h], dsk = d_skip ? d_skip[h] : 0.f;
-  for (int e = threadIdx.x; e < 2 * kChunk * NS; e += kScanThreads)       // the padding past `nstate` stays zero
-    (&Bs[0][0][0])[e] = (&Cs[0][0][0])[e] = 0.f;
+  if (nstate < NS)                                                        // the padding past `nstate` stays zero
+    for (int e = threadIdx.x; e < 2 * kChunk * NS; e += kScanThreads) (&Bs[0][0][0])[e] = (&Cs[0][0][0])[e] = 0.f;
   for (int e = threadIdx.x; e < 2 * kChunk * kScanCols; e += kScanThreads) (&xs[0][0][0])[e] = 0.f;
   __syncthreads();
   // raw rows of one pass -> buffer `buf` (asynchronous; committed as one group)
