@@ -674,12 +674,57 @@ void b200_runner_set_tp_fused(b200_runner*, int32_t on);
 #define B200_MIXER_LATENT_ATTN 0
 #define B200_MIXER_DELTA_RULE 1
 #define B200_MIXER_SSD 2
+#define B200_MIXER_WINDOW_ATTN 3            /* softmax attention, grouped K / V heads, paged K and V caches */
+#define B200_MIXER_DECAY_ATTN 4             /* linear attention with a decayed state (fixed or per-channel decay) */
+/* Layer layouts.  PARALLEL: mixer and feed-forward read ONE norm of the stream and add into it.  SANDWICH: every
+ * sublayer has a norm before and after it: x += post_norm(mixer(norm(x))), then x += ff_post_norm(ff(ff_norm(x))).
+ * In both a layer may have a SIDE mixer (b200_hybrid_set_layer_side) that reads the same normed input; the mixers'
+ * outputs are summed, each times its out_scale.                                                                   */
+#define B200_LAYOUT_PARALLEL 0
+#define B200_LAYOUT_SANDWICH 1
 
 void b200_resid_rmsnorm(void* out, const float* x, const float* w, int32_t num_tokens, int32_t width, float eps,
                         float w_offset, int32_t dt, int64_t stream);
+/* gate_act: 0 SiLU, 1 sigmoid; w may be NULL (no weight) */
 void b200_gated_group_norm(void* out, const float* y, int32_t ldy, const float* gate, int32_t ldg, const float* w,
                            int32_t w_period, int32_t num_tokens, int32_t channels, int32_t group, float eps,
-                           int32_t gate_first, int32_t dt, int64_t stream);
+                           int32_t gate_first, int32_t gate_act, int32_t dt, int64_t stream);
+/* x fp32 [T, width] += y / sqrt(mean(y^2) + eps) * (w_offset + w): the norm after a sublayer and its residual sum */
+void b200_resid_add_rmsnorm(float* x, const float* y, const float* w, int32_t num_tokens, int32_t width, float eps,
+                            float w_offset, int64_t stream);
+/* Windowed softmax attention with grouped K / V heads (csrc/window_attn.cu).  proj fp32 [T, ld] = [q: heads x dim |
+ * k: kv_heads x dim | v: kv_heads x vdim | ...]; bias fp32 over q | k | v or NULL; q_norm_w / k_norm_w fp32 over the WHOLE
+ * q / k projection or NULL (no norm); the first rot_dims entries of every q and k head are rotated as interleaved
+ * pairs by position * rot_freq[i] (f64 [rot_dims / 2]).  Writes q_out fp32 [T, heads, dim] and the cache rows
+ * k_cache [num_blocks, 64, kv_heads, dim], v_cache [num_blocks, 64, kv_heads, vdim] (dtype dt) at slot_mapping[t].  */
+void b200_window_attn_prep(const float* proj, int32_t ld, const float* bias, const float* q_norm_w,
+                           const float* k_norm_w, const double* rot_freq, const int64_t* positions,
+                           const int64_t* slot_mapping, float* q_out, void* k_cache, void* v_cache, int32_t num_tokens,
+                           int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t rot_dims, float eps,
+                           int32_t dt, int64_t stream);
+/* out [T, heads, vdim] (dtype dt).  Position i sees j <= i with i - j < window or j < keep_first (window <= 0: all);
+ * score = cap * tanh(q.k * scale / cap) (softcap <= 0: no cap); sink fp32 [heads] joins the denominator (NULL: none);
+ * gate fp32 [T, ld_gate]: head h's output is multiplied by sigmoid(gate[t, h]) (NULL: none).  workspace (may be NULL):
+ * b200_window_attn_workspace_bytes() bytes; with it steps of few rows split a row's keys over several blocks.     */
+void b200_window_attn(void* out, const float* q, const void* k_cache, const void* v_cache, const float* sink,
+                      const float* gate, int32_t ld_gate, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                      const uint32_t* block_tables, int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens,
+                      int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t window, int32_t keep_first,
+                      float scale, float softcap, int32_t dt, void* workspace, int64_t stream);
+int64_t b200_window_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t vdim,
+                                         int32_t window, int32_t keep_first);
+/* out fp32 [T, channels] = sigmoid(bias + low w2^T)^(1 / tau); low fp32 [T, rank] (row stride ld_low), w2 fp32
+ * [channels, rank], bias fp32 [channels] or NULL.                                                                  */
+void b200_lowrank_decay(float* out, const float* low, int32_t ld_low, const float* w2, const float* bias, float tau,
+                        int32_t num_tokens, int32_t channels, int32_t rank, int64_t stream);
+/* Linear attention with a decayed state: S <- diag(a_t) S + (k_scale k_t) v_t^T, o_t = S^T (q_scale q_t).  q, k fp32
+ * [T, heads, dim], v [T, heads, vdim] (row stride ld); exactly one of head_decay fp32 [heads] (a constant per head)
+ * and chan_decay fp32 [T, heads, dim] (row stride ld_decay); act != 0: SiLU on q, k and v first; out fp32
+ * [T, heads, vdim]; state fp32 [slots, heads, dim, vdim].                                                          */
+void b200_decay_attn(float* out, const float* q, const float* k, const float* v, int32_t ld, const float* head_decay,
+                     const float* chan_decay, int32_t ld_decay, float q_scale, float k_scale, int32_t act, float* state,
+                     const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                     int32_t num_seqs, int32_t heads, int32_t dim, int32_t vdim, int64_t stream);
 /* qc fp32 [T, ldq] = [q (heads x (dim + rot_dim)) | latent (kv_rank) | shared rotated key (rot_dim)] -> cache row at
  * slot_mapping[t] ([normed latent | rotated key], dtype dt), q_plain [T, heads, dim] (dtype dt) and the rotated query
  * parts in q_full [T, heads, kv_rank + rot_dim] fp32 (entries kv_rank.. of every head).  rot_freq f64 [rot_dims / 2]. */
@@ -730,6 +775,7 @@ typedef struct b200_hybrid_config {
   int32_t max_seqs, max_tokens;             /* per step */
   int32_t num_state_slots;
   float norm_eps, norm_weight_offset;       /* layer / final norms multiply by (offset + w) */
+  float embed_scale;                        /* the embedding row is multiplied by it (0 = 1) */
 } b200_hybrid_config;
 
 typedef struct b200_hybrid_layer {
@@ -751,12 +797,35 @@ typedef struct b200_hybrid_layer {
   const double* rot_freq;                   /* f64 [rot_dims / 2], device */
   const void *w_router, *w_gate_up, *w_down, *w_shared_gate_up, *w_shared_down;
   void *kv_cache, *conv_state, *rec_state;  /* caller-owned pools (see the kernels above for their shapes) */
+  /* ---- layouts, side mixers, windowed attention and decayed linear attention */
+  int32_t layout;                           /* B200_LAYOUT_*; SANDWICH: shared_ff is the dense gated feed-forward
+                                               (w_shared_gate_up / w_shared_down), read through ff_norm_w */
+  int32_t keep_first;                       /* window attention: the first keep_first positions stay visible */
+  int32_t qkv_act;                          /* decay attention: != 0 SiLU on q, k and v */
+  int32_t gate_act;                         /* decay attention output gate: 0 SiLU, 1 sigmoid */
+  int32_t decay_rank;                       /* decay attention: > 0: per-channel decay from a low-rank projection */
+  int32_t out_norm_period;                  /* decay attention: elements of out_norm_w (0: the norm has no weight);
+                                               norm_groups = groups the heads x vdim outputs are normalised in */
+  float softcap, q_scale, k_scale, decay_tau, out_scale;    /* scales of 0 mean 1 */
+  /* w_in of the new mixers:
+   *   window attention: [q: heads x dim | k: kv_heads x dim | v: kv_heads x vdim | gate: heads (if gated)]
+   *   decay attention:  [q: heads x dim | k: heads x dim | v: heads x vdim | gate: heads x vdim | low: decay_rank] */
+  const void *post_norm_w, *ff_norm_w, *ff_post_norm_w;     /* fp32 [width], SANDWICH layout */
+  const void *in_bias, *o_bias;             /* fp32: over q | k | v of window attention; over the o-projection's outputs */
+  const void *q_norm_w, *k_norm_w;          /* fp32, whole-projection norms of window attention (NULL: none) */
+  const void *head_decay;                   /* fp32 [heads] (decay_rank == 0) */
+  const void *w_decay2, *decay_bias;        /* fp32 [heads x dim, decay_rank], [heads x dim] */
+  int32_t gated;                            /* window attention: != 0: per-head sigmoid output gate, logits last in w_in */
+  void* v_cache;                            /* window attention: kv_cache holds K, v_cache V */
 } b200_hybrid_layer;
 
 typedef struct b200_hybrid b200_hybrid;
 b200_hybrid* b200_hybrid_new(const b200_hybrid_config* cfg);
 void b200_hybrid_free(b200_hybrid*);
 void b200_hybrid_set_layer(b200_hybrid*, int32_t layer, const b200_hybrid_layer* l);
+/* A second mixer of the layer, beside the first: it reads the same normed input and its output (times out_scale) joins
+ * the first one's.  Only the mixer's own fields of `side` are used (no norms, no feed-forward).  After set_layer.    */
+void b200_hybrid_set_layer_side(b200_hybrid*, int32_t layer, const b200_hybrid_layer* side);
 /* embed [vocab, width], lm_head [vocab, width] in dtype dt; final_norm fp32 [width] */
 void b200_hybrid_set_globals(b200_hybrid*, const void* embed, const void* final_norm, const void* lm_head);
 int64_t b200_hybrid_workspace_bytes(const b200_hybrid*);

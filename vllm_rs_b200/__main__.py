@@ -23,7 +23,7 @@ def _generate(a) -> int:
     cfg, tensors = read_model_dir(a.model)
     arch = models.architecture_of(cfg)
     if not _lib.LIB_PATH.exists() and not _lib.HYBRID_LIB_PATH.exists():
-        build.build(verbose=False, target="hybrid" if arch == "Fidasun" else "full")
+        build.build(verbose=False, target="hybrid" if arch in models.HYBRID_ARCHITECTURES else "full")
     prompts = [[int(x) for x in p.split(",") if x.strip()] for p in a.prompt_ids]
     longest = max(len(p) for p in prompts) + a.max_new_tokens
     per_seq = (longest + 63) // 64 + 2

@@ -51,7 +51,7 @@ class HybridConfig(C.Structure):
 
     _fields_ = [(n, c_i32) for n in ("width", "vocab", "num_layers", "dt", "block_size", "num_blocks",
                                      "max_blocks_per_seq", "max_seqs", "max_tokens", "num_state_slots")] + \
-               [("norm_eps", c_f32), ("norm_weight_offset", c_f32)]
+               [("norm_eps", c_f32), ("norm_weight_offset", c_f32), ("embed_scale", c_f32)]
 
 
 class HybridLayer(C.Structure):
@@ -64,7 +64,12 @@ class HybridLayer(C.Structure):
                [(n, c_vp) for n in ("norm_w", "w_in", "w_uk", "w_uv", "w_o", "latent_norm_w", "sink", "conv_w", "conv_b",
                                     "a_log", "dt_bias", "d_skip", "out_norm_w", "rot_freq", "w_router", "w_gate_up",
                                     "w_down", "w_shared_gate_up", "w_shared_down", "kv_cache", "conv_state",
-                                    "rec_state")]
+                                    "rec_state")] + \
+               [(n, c_i32) for n in ("layout", "keep_first", "qkv_act", "gate_act", "decay_rank", "out_norm_period")] + \
+               [(n, c_f32) for n in ("softcap", "q_scale", "k_scale", "decay_tau", "out_scale")] + \
+               [(n, c_vp) for n in ("post_norm_w", "ff_norm_w", "ff_post_norm_w", "in_bias", "o_bias", "q_norm_w",
+                                    "k_norm_w", "head_decay", "w_decay2", "decay_bias")] + \
+               [("gated", c_i32), ("v_cache", c_vp)]
 
 
 class KvCachePlan(C.Structure):
@@ -234,7 +239,13 @@ _SIGS = {
     "b200_comm_world": (c_i32, [c_vp]),
     # hybrid decoders with an fp32 residual stream
     "b200_resid_rmsnorm": (None, [c_vp] * 3 + [c_i32, c_i32, c_f32, c_f32, c_i32, c_i64]),
-    "b200_gated_group_norm": (None, [c_vp, c_vp, c_i32, c_vp, c_i32, c_vp] + [c_i32] * 4 + [c_f32, c_i32, c_i32, c_i64]),
+    "b200_gated_group_norm": (None, [c_vp, c_vp, c_i32, c_vp, c_i32, c_vp] + [c_i32] * 4 + [c_f32, c_i32, c_i32, c_i32, c_i64]),
+    "b200_resid_add_rmsnorm": (None, [c_vp] * 3 + [c_i32, c_i32, c_f32, c_f32, c_i64]),
+    "b200_window_attn_prep": (None, [c_vp, c_i32] + [c_vp] * 9 + [c_i32] * 6 + [c_f32, c_i32, c_i64]),
+    "b200_window_attn": (None, [c_vp] * 6 + [c_i32] + [c_vp] * 3 + [c_i32] * 9 + [c_f32, c_f32, c_i32, c_vp, c_i64]),
+    "b200_window_attn_workspace_bytes": (c_i64, [c_i32] * 6),
+    "b200_lowrank_decay": (None, [c_vp, c_vp, c_i32, c_vp, c_vp, c_f32, c_i32, c_i32, c_i32, c_i64]),
+    "b200_decay_attn": (None, [c_vp] * 4 + [c_i32, c_vp, c_vp, c_i32, c_f32, c_f32, c_i32] + [c_vp] * 4 + [c_i32] * 4 + [c_i64]),
     "b200_latent_prep": (None, [c_vp, c_i32] + [c_vp] * 5 + [c_f32, c_vp, c_vp] + [c_i32] * 6 + [c_f32, c_i32, c_i64]),
     "b200_latent_attn": (None, [c_vp] * 7 + [c_i32] * 7 + [c_f32, c_i32, c_vp, c_i64]),
     "b200_latent_attn_workspace_bytes": (c_i64, [c_i32] * 4),
@@ -247,6 +258,7 @@ _SIGS = {
     "b200_hybrid_new": (c_vp, [C.POINTER(HybridConfig)]),
     "b200_hybrid_free": (None, [c_vp]),
     "b200_hybrid_set_layer": (None, [c_vp, c_i32, C.POINTER(HybridLayer)]),
+    "b200_hybrid_set_layer_side": (None, [c_vp, c_i32, C.POINTER(HybridLayer)]),
     "b200_hybrid_set_globals": (None, [c_vp] * 4),
     "b200_hybrid_workspace_bytes": (c_i64, [c_vp]),
     "b200_hybrid_set_workspace": (None, [c_vp, c_vp, c_i64]),

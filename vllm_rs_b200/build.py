@@ -35,7 +35,8 @@ NVCC_FLAGS = [
 ] + os.environ.get("B200_NVCC_EXTRA", "").split()   # e.g. -DB200_DEC_TRACE (tools/dec_trace.py)
 
 
-HYBRID_SOURCES = ["runtime.cu", "glue.cu", "sampler.cu", "seq_norms.cu", "latent_attn.cu", "linear_recurrence.cu",
+HYBRID_SOURCES = ["runtime.cu", "glue.cu", "sampler.cu", "seq_norms.cu", "latent_attn.cu", "window_attn.cu",
+                  "linear_recurrence.cu",
                   "moe.cu", "gemm_lib.cu", "host/scheduler.cpp", "host/hybrid_runner.cpp"]
 HYBRID_LIB = PKG / "libb200_hybrid.so"
 

@@ -32,6 +32,12 @@ static cublasHandle_t handle() {
 bool gemm_f32out(const void* a, int lda, long long stride_a, const void* w, int ldw, long long stride_w, float* c,
                  int ldc, long long stride_c, int M, int N, int K, int batch, float beta, int w_kn, int dt,
                  cudaStream_t st) {
+  return gemm_f32out_scaled(a, lda, stride_a, w, ldw, stride_w, c, ldc, stride_c, M, N, K, batch, 1.f, beta, w_kn, dt, st);
+}
+
+bool gemm_f32out_scaled(const void* a, int lda, long long stride_a, const void* w, int ldw, long long stride_w, float* c,
+                        int ldc, long long stride_c, int M, int N, int K, int batch, float alpha, float beta, int w_kn,
+                        int dt, cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return true;
   cublasHandle_t h = handle();
   if (!h) {
@@ -44,7 +50,6 @@ bool gemm_f32out(const void* a, int lda, long long stride_a, const void* w, int 
     cudaGetDevice(&dev);       // setting the stream drops the user workspace: give it back (keeps the call capturable)
     if (g_ws[dev]) cublasSetWorkspace(h, g_ws[dev], 32u << 20);
   }
-  const float alpha = 1.f;
   const cudaDataType_t in = dt ? CUDA_R_32F : CUDA_R_16BF;
   const cublasComputeType_t comp = dt ? CUBLAS_COMPUTE_32F_PEDANTIC : CUBLAS_COMPUTE_32F;
   const cublasOperation_t opw = w_kn ? CUBLAS_OP_N : CUBLAS_OP_T;

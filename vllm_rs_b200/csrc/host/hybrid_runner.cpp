@@ -13,9 +13,17 @@
 //                      gated_group_norm (gate after the norm) ; x += . W_o^T
 //   SSD:               [z | x | B | C | dt] = h W_in^T ; short_conv_silu on x | B | C ; ssd_scan ;
 //                      gated_group_norm (gate before the norm) ; x += . W_o^T
+//   window attention:  [q | k | v | gate] = h W_in^T ; window_attn_prep (biases, whole-projection q / k norms, rotary,
+//                      K / V cache write) ; window_attn (window + kept first tokens, capped scores, sink, gate) ;
+//                      dst (+)= scale . W_o^T (+ bias)
+//   decay attention:   [q | k | v | gate | low] = h W_in^T ; lowrank_decay (per-channel decays) ; decay_attn ;
+//                      gated_group_norm ; dst (+)= scale . W_o^T
 //   experts:           router GEMM (fp32 out) -> moe_route -> sort -> grouped gate|up (SiLU * mul) -> grouped down ->
 //                      combine into x ; shared expert: GEMM, silu_mul, GEMM with beta = 1 into x
 // The residual add of every branch is the beta = 1 accumulation of its last matrix product (or the combine kernel).
+// Sandwich layer (a norm before AND after each sublayer): the mixers of the layer (one, or two side by side with their
+// scales) write their sum into y, then x += post_norm(y) (resid_add_rmsnorm); the dense gated feed-forward reads
+// ff_norm(x), writes y, and x += ff_post_norm(y).
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -42,11 +50,13 @@ inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 struct b200_hybrid {
   b200_hybrid_config cfg;
   std::vector<b200_hybrid_layer> layers;
+  std::vector<b200_hybrid_layer> sides;      // side mixer of layer i (sides[i].heads == 0: none)
   const void *embed = nullptr, *final_norm = nullptr, *lm_head = nullptr;
   uint8_t* ws = nullptr;
   float* trace = nullptr;
   // workspace carve-up
   float* x = nullptr;          // [T, width] residual stream
+  float* y = nullptr;          // [T, width] output of a sublayer before the norm that follows it (sandwich layers)
   void* h = nullptr;           // [T, width] normed stream, operand dtype
   float* proj = nullptr;       // [T, max fused input projection]
   float* conv = nullptr;       // [T, max convolved channels]: output of the short convolution
@@ -101,6 +111,8 @@ static int in_rows(const b200_hybrid_layer& l) {
   switch (l.mixer) {
     case B200_MIXER_LATENT_ATTN: return l.heads * (l.dim + l.rot_dim) + l.kv_rank + l.rot_dim;
     case B200_MIXER_DELTA_RULE: return 2 * l.kv_heads * l.dim + 2 * l.heads * l.vdim + 2 * l.heads;
+    case B200_MIXER_WINDOW_ATTN: return l.heads * l.dim + l.kv_heads * (l.dim + l.vdim) + (l.gated ? l.heads : 0);
+    case B200_MIXER_DECAY_ATTN: return 2 * l.heads * l.dim + 2 * l.heads * l.vdim + l.decay_rank;
     default: return 2 * l.heads * l.vdim + 2 * l.kv_heads * l.state + l.heads;
   }
 }
@@ -111,9 +123,22 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
   size_t conv_n = 1, proj_n = 1, aux_n = 1, opa_n = 1, lat_n = 1, E = 1, top = 1, sh_n = 1, moe_bytes = 256, attn_bytes = 0;
   // rows up to which a step may split its attention rows: beyond two blocks per SM a split is never chosen
   r->attn_ws_rows = std::min<size_t>(T, 2 * static_cast<size_t>(sm_count()));
-  for (const b200_hybrid_layer& l : r->layers) {
+  std::vector<b200_hybrid_layer> all(r->layers);
+  for (const b200_hybrid_layer& l : r->sides)
+    if (l.heads > 0) all.push_back(l);
+  for (const b200_hybrid_layer& l : all) {
     proj_n = std::max<size_t>(proj_n, in_rows(l));
-    if (l.mixer == B200_MIXER_LATENT_ATTN) {
+    if (l.mixer == B200_MIXER_WINDOW_ATTN) {
+      aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * l.dim);
+      opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * l.vdim);
+      for (size_t rows = 1; rows <= r->attn_ws_rows; ++rows)
+        attn_bytes = std::max(attn_bytes, window_attn_workspace_bytes(static_cast<int>(rows), l.heads, l.kv_heads, l.vdim,
+                                                                      l.window, l.keep_first));
+    } else if (l.mixer == B200_MIXER_DECAY_ATTN) {
+      aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * l.vdim);
+      opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * l.vdim);
+      if (l.decay_rank > 0) conv_n = std::max<size_t>(conv_n, static_cast<size_t>(l.heads) * l.dim);
+    } else if (l.mixer == B200_MIXER_LATENT_ATTN) {
       aux_n = std::max<size_t>(aux_n, static_cast<size_t>(l.heads) * std::max(l.kv_rank + l.rot_dim, l.vdim));
       opa_n = std::max<size_t>(opa_n, static_cast<size_t>(l.heads) * std::max(l.dim, l.vdim));
       lat_n = std::max<size_t>(lat_n, static_cast<size_t>(l.heads) * l.kv_rank);
@@ -140,6 +165,7 @@ static int64_t carve(b200_hybrid* r, uint8_t* base) {
     return p;
   };
   r->x = (float*)take(T * c.width * 4);
+  r->y = (float*)take(T * c.width * 4);
   r->h = take(T * c.width * es);
   r->proj = (float*)take(T * proj_n * 4);
   r->conv = (float*)take(T * conv_n * 4);
@@ -178,8 +204,11 @@ b200_hybrid* b200_hybrid_new(const b200_hybrid_config* cfg) {
   }
   auto* r = new b200_hybrid();
   r->cfg = *cfg;
+  if (r->cfg.embed_scale == 0.f) r->cfg.embed_scale = 1.f;
   r->layers.resize(cfg->num_layers);
+  r->sides.resize(cfg->num_layers);
   std::memset(r->layers.data(), 0, sizeof(b200_hybrid_layer) * cfg->num_layers);
+  std::memset(r->sides.data(), 0, sizeof(b200_hybrid_layer) * cfg->num_layers);
   return r;
 }
 
@@ -189,13 +218,50 @@ void b200_hybrid_free(b200_hybrid* r) {
   delete r;
 }
 
+// the mixer's own fields (shared by a layer's first mixer and its side mixer)
+static bool mixer_ok(const b200_hybrid_layer* l) {
+  bool ok = l->heads > 0 && l->vdim > 0 && l->w_in && l->w_o;
+  if (l->mixer == B200_MIXER_WINDOW_ATTN)
+    return ok && l->kv_heads > 0 && l->heads % l->kv_heads == 0 && l->dim > 0 && l->rot_dims % 2 == 0 &&
+           l->rot_dims <= l->dim && (l->rot_dims == 0 || l->rot_freq) && l->kv_cache && l->v_cache;
+  if (l->mixer == B200_MIXER_DECAY_ATTN)
+    return ok && l->dim > 0 && l->dim <= 256 && l->rec_state && l->norm_groups > 0 &&
+           (l->heads * l->vdim) % l->norm_groups == 0 && (l->out_norm_period == 0 || l->out_norm_w) &&
+           (l->decay_rank > 0 ? (l->w_decay2 && l->decay_tau > 0.f) : l->head_decay != nullptr);
+  return false;
+}
+static void default_scales(b200_hybrid_layer& l) {
+  if (l.q_scale == 0.f) l.q_scale = 1.f;
+  if (l.k_scale == 0.f) l.k_scale = 1.f;
+  if (l.out_scale == 0.f) l.out_scale = 1.f;
+}
+
+void b200_hybrid_set_layer_side(b200_hybrid* r, int32_t layer, const b200_hybrid_layer* side) {
+  if (layer < 0 || layer >= r->cfg.num_layers || !side) {
+    set_error(1, "hybrid_set_layer_side: layer out of range");
+    return;
+  }
+  if (!mixer_ok(side)) {
+    set_error(1, "hybrid_set_layer_side: a side mixer is windowed attention or decayed linear attention, fully described");
+    return;
+  }
+  r->sides[layer] = *side;
+  default_scales(r->sides[layer]);
+}
+
 void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_layer* l) {
   if (layer < 0 || layer >= r->cfg.num_layers || !l) {
     set_error(1, "hybrid_set_layer: layer out of range");
     return;
   }
   bool ok = l->heads > 0 && l->vdim > 0 && l->norm_w && l->w_in && l->w_o;
-  if (l->mixer == B200_MIXER_LATENT_ATTN)
+  if (l->layout == B200_LAYOUT_SANDWICH)
+    ok = ok && l->post_norm_w && l->experts == 0 && (l->shared_ff == 0 || (l->ff_norm_w && l->ff_post_norm_w));
+  else
+    ok = ok && l->layout == B200_LAYOUT_PARALLEL;
+  if (l->mixer == B200_MIXER_WINDOW_ATTN || l->mixer == B200_MIXER_DECAY_ATTN)
+    ok = ok && mixer_ok(l);
+  else if (l->mixer == B200_MIXER_LATENT_ATTN)
     ok = ok && l->kv_rank > 0 && l->w_uk && l->w_uv && l->latent_norm_w && l->kv_cache && l->rot_dims % 2 == 0 &&
          l->rot_dims <= l->rot_dim && (l->rot_dims == 0 || l->rot_freq);
   else if (l->mixer == B200_MIXER_DELTA_RULE)
@@ -214,6 +280,7 @@ void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_laye
     return;
   }
   r->layers[layer] = *l;
+  default_scales(r->layers[layer]);
 }
 
 void b200_hybrid_set_globals(b200_hybrid* r, const void* embed, const void* final_norm, const void* lm_head) {
@@ -226,6 +293,7 @@ int64_t b200_hybrid_workspace_bytes(const b200_hybrid* r) {
   b200_hybrid tmp;
   tmp.cfg = r->cfg;
   tmp.layers = r->layers;
+  tmp.sides = r->sides;
   return carve(&tmp, nullptr) + 256;
 }
 
@@ -270,7 +338,7 @@ int64_t b200_hybrid_launches_per_step(const b200_hybrid* r) { return r->launches
 
 static void mixer_latent(b200_hybrid* r, const b200_hybrid_layer& l, const int64_t* positions, const int64_t* slots,
                          const uint32_t* cu, const uint32_t* ctx, const uint32_t* bt, int max_blocks, int B, int T,
-                         cudaStream_t st) {
+                         float* dst, float alpha, float beta, cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, R = l.kv_rank + l.rot_dim, n_in = in_rows(l);
   gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
@@ -293,11 +361,12 @@ static void mixer_latent(b200_hybrid* r, const b200_hybrid_layer& l, const int64
     launch_cast_rows(r->opa, r->aux, H * l.vdim, T, H * l.vdim, 0, st);
     o_in = r->opa;
   }
-  gemm_f32out(o_in, H * l.vdim, 0, l.w_o, H * l.vdim, 0, r->x, c.width, 0, T, c.width, H * l.vdim, 1, 1.f, 0, c.dt, st);
+  gemm_f32out_scaled(o_in, H * l.vdim, 0, l.w_o, H * l.vdim, 0, dst, c.width, 0, T, c.width, H * l.vdim, 1, alpha, beta, 0,
+                     c.dt, st);
 }
 
 static void mixer_delta(b200_hybrid* r, const b200_hybrid_layer& l, const uint32_t* cu, const uint32_t* ctx,
-                        const int32_t* state_slots, int B, int T, cudaStream_t st) {
+                        const int32_t* state_slots, int B, int T, float* dst, float alpha, float beta, cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, Hk = l.kv_heads, n_in = in_rows(l);
   const int nq = Hk * l.dim, nv = H * l.vdim, nconv = 2 * nq + nv;
@@ -313,12 +382,12 @@ static void mixer_delta(b200_hybrid* r, const b200_hybrid_layer& l, const uint32
   launch_delta_rule(r->aux, q, k, v, nconv, b_raw, a_raw, n_in, (const float*)l.a_log, (const float*)l.dt_bias,
                     (float*)l.rec_state, state_slots, cu, ctx, B, H, Hk, l.dim, l.vdim, st);
   launch_gated_group_norm(r->opa, r->aux, nv, gate, n_in, (const float*)l.out_norm_w, l.vdim, T, nv, l.vdim, c.norm_eps,
-                          0, c.dt, st);
-  gemm_f32out(r->opa, nv, 0, l.w_o, nv, 0, r->x, c.width, 0, T, c.width, nv, 1, 1.f, 0, c.dt, st);
+                          0, 0, c.dt, st);
+  gemm_f32out_scaled(r->opa, nv, 0, l.w_o, nv, 0, dst, c.width, 0, T, c.width, nv, 1, alpha, beta, 0, c.dt, st);
 }
 
 static void mixer_ssd(b200_hybrid* r, const b200_hybrid_layer& l, const uint32_t* cu, const uint32_t* ctx,
-                      const int32_t* state_slots, int B, int T, cudaStream_t st) {
+                      const int32_t* state_slots, int B, int T, float* dst, float alpha, float beta, cudaStream_t st) {
   const b200_hybrid_config& c = r->cfg;
   const int H = l.heads, G = l.kv_heads, N = l.state, inner = H * l.vdim, n_in = in_rows(l);
   const int nconv = inner + 2 * G * N;
@@ -330,8 +399,76 @@ static void mixer_ssd(b200_hybrid* r, const b200_hybrid_layer& l, const uint32_t
                   (const float*)l.dt_bias, (const float*)l.d_skip, (float*)l.rec_state, state_slots, cu, ctx, B, H, G, N,
                   l.vdim, st);
   launch_gated_group_norm(r->opa, r->aux, inner, r->proj, n_in, (const float*)l.out_norm_w, inner, T, inner,
-                          inner / l.norm_groups, c.norm_eps, 1, c.dt, st);
-  gemm_f32out(r->opa, inner, 0, l.w_o, inner, 0, r->x, c.width, 0, T, c.width, inner, 1, 1.f, 0, c.dt, st);
+                          inner / l.norm_groups, c.norm_eps, 1, 0, c.dt, st);
+  gemm_f32out_scaled(r->opa, inner, 0, l.w_o, inner, 0, dst, c.width, 0, T, c.width, inner, 1, alpha, beta, 0, c.dt, st);
+}
+
+static void mixer_window(b200_hybrid* r, const b200_hybrid_layer& l, const int64_t* positions, const int64_t* slots,
+                         const uint32_t* cu, const uint32_t* ctx, const uint32_t* bt, int max_blocks, int B, int T,
+                         float* dst, float alpha, float beta, cudaStream_t st) {
+  const b200_hybrid_config& c = r->cfg;
+  const int H = l.heads, G = l.kv_heads, n_in = in_rows(l), nv = H * l.vdim;
+  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  launch_window_attn_prep(r->proj, n_in, (const float*)l.in_bias, (const float*)l.q_norm_w, (const float*)l.k_norm_w,
+                          l.rot_freq, positions, slots, r->aux, l.kv_cache, l.v_cache, T, H, G, l.dim, l.vdim, l.rot_dims,
+                          c.norm_eps, c.dt, st);
+  const float* gate = l.gated ? r->proj + H * l.dim + G * (l.dim + l.vdim) : nullptr;
+  launch_window_attn(r->opa, r->aux, l.kv_cache, l.v_cache, (const float*)l.sink, gate, n_in, cu, ctx, bt, max_blocks, B,
+                     T, H, G, l.dim, l.vdim, l.window, l.keep_first, l.scale, l.softcap, c.dt,
+                     static_cast<size_t>(T) <= r->attn_ws_rows ? r->attn_ws : nullptr, st);
+  gemm_f32out_scaled(r->opa, nv, 0, l.w_o, nv, 0, dst, c.width, 0, T, c.width, nv, 1, alpha, beta, 0, c.dt, st);
+  if (l.o_bias) launch_bias_rows(dst, (const float*)l.o_bias, alpha, T, c.width, st);
+}
+
+static void mixer_decay(b200_hybrid* r, const b200_hybrid_layer& l, const uint32_t* cu, const uint32_t* ctx,
+                        const int32_t* state_slots, int B, int T, float* dst, float alpha, float beta, cudaStream_t st) {
+  const b200_hybrid_config& c = r->cfg;
+  const int H = l.heads, nk = H * l.dim, nv = H * l.vdim, n_in = in_rows(l);
+  gemm_f32out(r->h, c.width, 0, l.w_in, c.width, 0, r->proj, n_in, 0, T, n_in, c.width, 1, 0.f, 0, c.dt, st);
+  const float* q = r->proj;
+  const float* k = q + nk;
+  const float* v = k + nk;
+  const float* gate = v + nv;
+  const float* chan = nullptr;
+  if (l.decay_rank > 0) {
+    launch_lowrank_decay(r->conv, gate + nv, n_in, (const float*)l.w_decay2, (const float*)l.decay_bias, l.decay_tau, T,
+                         nk, l.decay_rank, st);
+    chan = r->conv;
+  }
+  launch_decay_attn(r->aux, q, k, v, n_in, chan ? nullptr : (const float*)l.head_decay, chan, nk, l.q_scale, l.k_scale,
+                    l.qkv_act, (float*)l.rec_state, state_slots, cu, ctx, B, H, l.dim, l.vdim, st);
+  launch_gated_group_norm(r->opa, r->aux, nv, gate, n_in, (const float*)(l.out_norm_period ? l.out_norm_w : nullptr),
+                          l.out_norm_period ? l.out_norm_period : 1, T, nv, nv / l.norm_groups, c.norm_eps, 0, l.gate_act,
+                          c.dt, st);
+  gemm_f32out_scaled(r->opa, nv, 0, l.w_o, nv, 0, dst, c.width, 0, T, c.width, nv, 1, alpha, beta, 0, c.dt, st);
+  if (l.o_bias) launch_bias_rows(dst, (const float*)l.o_bias, alpha, T, c.width, st);
+}
+
+// one mixer of a layer: dst = alpha * mixer(h) + beta * dst
+static void run_mixer(b200_hybrid* r, const b200_hybrid_layer& l, const int64_t* positions, const int64_t* slot_mapping,
+                      const uint32_t* cu, const uint32_t* ctx, const uint32_t* block_tables, const int32_t* state_slots,
+                      int max_blocks, int B, int T, float* dst, float alpha, float beta, cudaStream_t st) {
+  switch (l.mixer) {
+    case B200_MIXER_LATENT_ATTN:
+      mixer_latent(r, l, positions, slot_mapping, cu, ctx, block_tables, max_blocks, B, T, dst, alpha, beta, st);
+      break;
+    case B200_MIXER_DELTA_RULE: mixer_delta(r, l, cu, ctx, state_slots, B, T, dst, alpha, beta, st); break;
+    case B200_MIXER_WINDOW_ATTN:
+      mixer_window(r, l, positions, slot_mapping, cu, ctx, block_tables, max_blocks, B, T, dst, alpha, beta, st);
+      break;
+    case B200_MIXER_DECAY_ATTN: mixer_decay(r, l, cu, ctx, state_slots, B, T, dst, alpha, beta, st); break;
+    default: mixer_ssd(r, l, cu, ctx, state_slots, B, T, dst, alpha, beta, st); break;
+  }
+}
+
+// dense gated feed-forward of a sandwich layer: y = W_down (silu(W_gate h) * (W_up h))
+static void dense_ffn(b200_hybrid* r, const b200_hybrid_layer& l, int T, cudaStream_t st) {
+  const b200_hybrid_config& c = r->cfg;
+  gemm_f32out(r->h, c.width, 0, l.w_shared_gate_up, c.width, 0, r->sh, 2 * l.shared_ff, 0, T, 2 * l.shared_ff, c.width, 1,
+              0.f, 0, c.dt, st);
+  launch_silu_mul_f32(r->sha, r->sh, T, l.shared_ff, c.dt, st);
+  gemm_f32out(r->sha, l.shared_ff, 0, l.w_shared_down, l.shared_ff, 0, r->y, c.width, 0, T, c.width, l.shared_ff, 1, 0.f,
+              0, c.dt, st);
 }
 
 static void feed_forward(b200_hybrid* r, const b200_hybrid_layer& l, int T, cudaStream_t st) {
@@ -367,19 +504,34 @@ void b200_hybrid_step(b200_hybrid* r, const uint32_t* input_ids, const int64_t* 
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long launches0 = launch_count();
-  launch_embed_f32(r->x, r->embed, input_ids, T, c.width, c.vocab, c.dt, st);
+  launch_embed_f32(r->x, r->embed, input_ids, T, c.width, c.vocab, c.embed_scale, c.dt, st);
   for (int i = 0; i < c.num_layers; ++i) {
     const b200_hybrid_layer& l = r->layers[i];
+    const b200_hybrid_layer& side = r->sides[i];
     launch_resid_rmsnorm(r->h, r->x, (const float*)l.norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, nullptr,
                          c.dt, st);
-    switch (l.mixer) {
-      case B200_MIXER_LATENT_ATTN:
-        mixer_latent(r, l, positions, slot_mapping, cu, ctx, block_tables, max_blocks, B, T, st);
-        break;
-      case B200_MIXER_DELTA_RULE: mixer_delta(r, l, cu, ctx, state_slots, B, T, st); break;
-      default: mixer_ssd(r, l, cu, ctx, state_slots, B, T, st); break;
+    if (l.layout == B200_LAYOUT_SANDWICH) {
+      run_mixer(r, l, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->y, l.out_scale,
+                0.f, st);
+      if (side.heads > 0)
+        run_mixer(r, side, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->y,
+                  side.out_scale, 1.f, st);
+      launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.post_norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, st);
+      if (l.shared_ff > 0) {
+        launch_resid_rmsnorm(r->h, r->x, (const float*)l.ff_norm_w, T, c.width, c.norm_eps, c.norm_weight_offset, nullptr,
+                             c.dt, st);
+        dense_ffn(r, l, T, st);
+        launch_resid_add_rmsnorm(r->x, r->y, (const float*)l.ff_post_norm_w, T, c.width, c.norm_eps,
+                                 c.norm_weight_offset, st);
+      }
+    } else {
+      run_mixer(r, l, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->x, l.out_scale,
+                1.f, st);
+      if (side.heads > 0)
+        run_mixer(r, side, positions, slot_mapping, cu, ctx, block_tables, state_slots, max_blocks, B, T, r->x,
+                  side.out_scale, 1.f, st);
+      feed_forward(r, l, T, st);
     }
-    feed_forward(r, l, T, st);
     if (r->trace)
       cudaMemcpyAsync(r->trace + static_cast<size_t>(i) * c.max_tokens * c.width, r->x,
                       static_cast<size_t>(T) * c.width * 4, cudaMemcpyDeviceToDevice, st);

@@ -12,7 +12,12 @@
 //                     g = exp(-exp(a_log) * softplus(a + dt_bias)).  state [slots, heads, dim, vdim].
 //   ssd_scan        : per head, S [nstate, vdim]:  dt = softplus(dt_raw + dt_bias);  S <- exp(-exp(a_log) dt) S + dt B x^T;
 //                     y = S^T C + D x.  state [slots, heads, nstate, vdim].
-// In both scans eight lanes share one column of S (one value channel), each holding every eighth row in registers,
+//   decay_attn      : per head, S [dim, vdim]:  S <- diag(a_t) S + k_t v_t^T;  o_t = S^T q_t  (linear attention with a decayed
+//                     state, no softmax or denominator).  a_t is one constant per head (retention-style fixed decays) or
+//                     one value per key channel and token (gated linear attention; lowrank_decay makes it from a
+//                     low-rank projection: sigmoid(z)^(1/tau)).  Optional SiLU on q, k, v and scales on q and k.
+//                     state [slots, heads, dim, vdim].
+// In the scans eight lanes share one column of S (one value channel), each holding every eighth row in registers,
 // and walk the sequence's tokens in order: the exact recurrence, no chunked reformulation, so a portion boundary
 // cannot change the arithmetic.  The tokens' inputs are staged in shared memory a pass at a time through two buffers
 // filled by cp.async, so the walk never waits for global memory.
@@ -317,6 +322,127 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
   }
 }
 
+
+// out[t, c] = sigmoid(z)^(1 / tau) with z = bias[c] + sum_r w2[c, r] * low[t, r]: the per-channel decay of gated linear
+// attention from the low-rank half of its projection.  Computed as exp(log sigmoid(z) / tau), all fp32.
+__global__ void lowrank_decay_kernel(float* __restrict__ out, const float* __restrict__ low, int ld_low,
+                                     const float* __restrict__ w2, const float* __restrict__ bias, float inv_tau, int C,
+                                     int rank) {
+  extern __shared__ float lr[];
+  const int t = blockIdx.x;
+  for (int r = threadIdx.x; r < rank; r += blockDim.x) lr[r] = low[static_cast<size_t>(t) * ld_low + r];
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float z = bias ? bias[c] : 0.f;
+    const float* w = w2 + static_cast<size_t>(c) * rank;
+    for (int r = 0; r < rank; ++r) z += w[r] * lr[r];
+    const float ls = z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
+    out[static_cast<size_t>(t) * C + c] = expf(ls * inv_tau);
+  }
+}
+
+// tokens per pass of the decayed-state scan: with a per-channel decay a third row set is staged, so half as many
+constexpr int decay_chunk_for(int rows, bool chan) { return chan ? (chunk_for(rows) > 16 ? 16 : chunk_for(rows) / 2) : chunk_for(rows); }
+
+// grid = (column blocks, heads, sequences); block = 128 threads = 16 columns x kRowSplit lanes, as the scans above.
+// CHAN: the decay is per key channel and token (chan_decay [T, heads, dim], row stride ld_decay); otherwise one
+// constant per head (head_decay [heads]).
+template <int DK, bool CHAN>
+__global__ void __launch_bounds__(128)
+decay_attn_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ k,
+                  const float* __restrict__ v, int ld, const float* __restrict__ head_decay,
+                  const float* __restrict__ chan_decay, int ld_decay, float q_scale, float k_scale, int act,
+                  float* __restrict__ state, const int32_t* __restrict__ slots, const uint32_t* __restrict__ cu,
+                  const uint32_t* __restrict__ ctx, int heads, int dim, int vdim) {
+  constexpr int RS = kRowSplit, NR = DK / RS, kChunk = decay_chunk_for(DK, CHAN);
+  __shared__ float ks[2][kChunk][DK], qs[2][kChunk][DK], as[CHAN ? 2 : 1][CHAN ? kChunk : 1][CHAN ? DK : 1],
+      vs[2][kChunk][kScanCols];
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int part = threadIdx.x % RS;
+  const int col = blockIdx.x * (blockDim.x / RS) + threadIdx.x / RS;
+  const bool live = col < vdim;
+  const int t0 = cu[b], t1 = cu[b + 1];
+  if (t1 <= t0) return;
+  const bool fresh = static_cast<int>(ctx[b]) == t1 - t0;
+  float* sp = state + ((static_cast<size_t>(slots[b]) * heads + h) * dim) * vdim + col;
+  float s[NR];
+#pragma unroll
+  for (int j = 0; j < NR; ++j) {
+    const int i = j * RS + part;
+    s[j] = (!fresh && live && i < dim) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
+  }
+  const float hd = CHAN ? 0.f : head_decay[h];
+  if (dim < DK) {                                                         // the padding past `dim` stays zero
+    for (int e = threadIdx.x; e < 2 * kChunk * DK; e += kScanThreads) (&ks[0][0][0])[e] = (&qs[0][0][0])[e] = 0.f;
+    if (CHAN)
+      for (int e = threadIdx.x; e < 2 * kChunk * DK; e += kScanThreads) (&as[0][0][0])[e] = 0.f;
+  }
+  for (int e = threadIdx.x; e < 2 * kChunk * kScanCols; e += kScanThreads) (&vs[0][0][0])[e] = 0.f;
+  __syncthreads();
+  auto fetch = [&](int c0, int buf) {
+    const int n = min(kChunk, t1 - c0);
+    for (int e = threadIdx.x; e < n * dim; e += kScanThreads) {
+      const int r = e / dim, i = e - r * dim;
+      cp_async4(&ks[buf][r][i], k + static_cast<size_t>(c0 + r) * ld + h * dim + i);
+      cp_async4(&qs[buf][r][i], q + static_cast<size_t>(c0 + r) * ld + h * dim + i);
+      if (CHAN) cp_async4(&as[buf][r][i], chan_decay + static_cast<size_t>(c0 + r) * ld_decay + h * dim + i);
+    }
+    for (int e = threadIdx.x; e < n * kScanCols; e += kScanThreads) {
+      const int r = e / kScanCols, c = blockIdx.x * kScanCols + e % kScanCols;
+      if (c < vdim) cp_async4(&vs[buf][r][e % kScanCols], v + static_cast<size_t>(c0 + r) * ld + h * vdim + c);
+    }
+    cp_async_commit();
+  };
+  fetch(t0, 0);
+  int buf = 0;
+  for (int c0 = t0; c0 < t1; c0 += kChunk, buf ^= 1) {
+    const int n = min(kChunk, t1 - c0);
+    if (c0 + kChunk < t1) {
+      fetch(c0 + kChunk, buf ^ 1);         // the other buffer's tokens were walked before the last barrier
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    // activation and scales of the pass, in place
+    for (int e = threadIdx.x; e < n * dim; e += kScanThreads) {
+      const int r = e / dim, i = e - r * dim;
+      const float kv = ks[buf][r][i], qv = qs[buf][r][i];
+      ks[buf][r][i] = (act ? silu_exact(kv) : kv) * k_scale;
+      qs[buf][r][i] = (act ? silu_exact(qv) : qv) * q_scale;
+    }
+    if (act)
+      for (int e = threadIdx.x; e < n * kScanCols; e += kScanThreads)
+        vs[buf][e / kScanCols][e % kScanCols] = silu_exact(vs[buf][e / kScanCols][e % kScanCols]);
+    __syncthreads();
+    for (int r = 0; r < n; ++r) {
+      const float vv = vs[buf][r][threadIdx.x / RS];
+      float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NR; j += 2) {
+        s[j] = (CHAN ? as[buf][r][j * RS + part] : hd) * s[j] + ks[buf][r][j * RS + part] * vv;
+        y0 += qs[buf][r][j * RS + part] * s[j];
+        if (j + 1 < NR) {
+          s[j + 1] = (CHAN ? as[buf][r][(j + 1) * RS + part] : hd) * s[j + 1] + ks[buf][r][(j + 1) * RS + part] * vv;
+          y1 += qs[buf][r][(j + 1) * RS + part] * s[j + 1];
+        }
+      }
+      float y = y0 + y1;
+#pragma unroll
+      for (int o = 1; o < RS; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (live && part == 0) out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = y;
+    }
+    __syncthreads();                       // this buffer is refilled by the next pass's fetch
+  }
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+      const int i = j * RS + part;
+      if (i < dim) sp[static_cast<size_t>(i) * vdim] = s[j];
+    }
+  }
+}
+
 void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const float* taps_w, const float* bias,
                             float* state, const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs,
                             int num_rows, int C, int taps, cudaStream_t st_) {
@@ -389,6 +515,43 @@ void launch_ssd_scan(float* out, const float* x, const float* Bm, const float* C
   B200_CUDA_LAUNCH_CHECK();
 }
 
+
+void launch_lowrank_decay(float* out, const float* low, int ld_low, const float* w2, const float* bias, float tau, int T,
+                          int C, int rank, cudaStream_t st_) {
+  if (T <= 0 || C <= 0) return;
+  lowrank_decay_kernel<<<T, 256, static_cast<size_t>(rank) * 4, st_>>>(out, low, ld_low, w2, bias, 1.f / tau, C, rank);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_decay_attn(float* out, const float* q, const float* k, const float* v, int ld, const float* head_decay,
+                       const float* chan_decay, int ld_decay, float q_scale, float k_scale, int act, float* state,
+                       const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads, int dim,
+                       int vdim, cudaStream_t st_) {
+  if (num_seqs <= 0) return;
+  const int th = kScanThreads;
+  const dim3 grid((vdim + kScanCols - 1) / kScanCols, heads, num_seqs);
+#define B200_DECAY2(DK, CH)                                                                                          \
+  decay_attn_kernel<DK, CH><<<grid, th, 0, st_>>>(out, q, k, v, ld, head_decay, chan_decay, ld_decay, q_scale, k_scale, \
+                                                  act, state, slots, cu, ctx, heads, dim, vdim)
+#define B200_DECAY(DK)          \
+  {                             \
+    if (chan_decay) B200_DECAY2(DK, true); \
+    else B200_DECAY2(DK, false);           \
+  }
+  if (dim <= 16) B200_DECAY(16)
+  else if (dim <= 32) B200_DECAY(32)
+  else if (dim <= 64) B200_DECAY(64)
+  else if (dim <= 128) B200_DECAY(128)
+  else if (dim <= 256) B200_DECAY(256)
+  else {
+    set_error(1, "decay_attn: key dimension above 256 is not supported");
+    return;
+  }
+#undef B200_DECAY
+#undef B200_DECAY2
+  B200_CUDA_LAUNCH_CHECK();
+}
+
 }  // namespace b200
 
 extern "C" {
@@ -419,5 +582,21 @@ void b200_ssd_scan(float* out, const float* x, const float* Bm, const float* Cm,
                  "ssd_scan: bad arguments");
   b200::launch_ssd_scan(out, x, Bm, Cm, ld, dt_raw, ld_dt, a_log, dt_bias, d_skip, state, state_slots, cu_seqlens_q,
                         context_lens, num_seqs, heads, groups, nstate, vdim, reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_lowrank_decay(float* out, const float* low, int32_t ld_low, const float* w2, const float* bias, float tau,
+                         int32_t num_tokens, int32_t channels, int32_t rank, int64_t stream) {
+  B200_CHECK_ARG(out && low && w2 && tau > 0.f && channels > 0 && rank > 0 && rank <= 8192, "lowrank_decay: bad arguments");
+  b200::launch_lowrank_decay(out, low, ld_low, w2, bias, tau, num_tokens, channels, rank,
+                             reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_decay_attn(float* out, const float* q, const float* k, const float* v, int32_t ld, const float* head_decay,
+                     const float* chan_decay, int32_t ld_decay, float q_scale, float k_scale, int32_t act, float* state,
+                     const int32_t* state_slots, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                     int32_t num_seqs, int32_t heads, int32_t dim, int32_t vdim, int64_t stream) {
+  B200_CHECK_ARG(out && q && k && v && ((head_decay != nullptr) != (chan_decay != nullptr)) && state && state_slots &&
+                     cu_seqlens_q && context_lens && heads > 0 && dim > 0 && vdim > 0,
+                 "decay_attn: bad arguments (exactly one of head_decay / chan_decay)");
+  b200::launch_decay_attn(out, q, k, v, ld, head_decay, chan_decay, ld_decay, q_scale, k_scale, act, state, state_slots,
+                          cu_seqlens_q, context_lens, num_seqs, heads, dim, vdim, reinterpret_cast<cudaStream_t>(stream));
 }
 }

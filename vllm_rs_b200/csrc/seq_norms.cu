@@ -12,12 +12,12 @@ using namespace seqmix;
 
 template <typename T>
 __global__ void embed_f32_kernel(float* __restrict__ x, const T* __restrict__ table, const uint32_t* __restrict__ ids,
-                                 int width, int vocab) {
+                                 int width, int vocab, float scale) {
   const int t = blockIdx.x;
   uint32_t id = ids[t];
   if (id >= static_cast<uint32_t>(vocab)) id = 0;
   const T* row = table + static_cast<size_t>(id) * width;
-  for (int d = threadIdx.x; d < width; d += blockDim.x) x[static_cast<size_t>(t) * width + d] = ld(row + d);
+  for (int d = threadIdx.x; d < width; d += blockDim.x) x[static_cast<size_t>(t) * width + d] = ld(row + d) * scale;
 }
 
 // out[r] = x[row(r)] / sqrt(mean(x^2) + eps) * (w_offset + w); rows == nullptr: row(r) = r
@@ -35,29 +35,52 @@ __global__ void resid_rmsnorm_kernel(T* __restrict__ out, const float* __restric
     st(out + static_cast<size_t>(r) * width + d, xr[d] * inv * (w_offset + w[d]));
 }
 
-// One block per (token, group of `group` channels).  gate_first: u = y * silu(g), out = u / rms(u) * w;
-// otherwise out = y / rms(y) * w * silu(g).  w is indexed by (channel % w_period).
+// One block per (token, group of `group` channels).  gate_first: u = y * act(g), out = u / rms(u) * w;
+// otherwise out = y / rms(y) * w * act(g).  w is indexed by (channel % w_period); w == nullptr: no weight.
+// act = SiLU (gate_act 0) or the logistic sigmoid (gate_act 1).
 template <typename T>
 __global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __restrict__ y, int ldy,
                                         const float* __restrict__ gate, int ldg, const float* __restrict__ w,
-                                        int w_period, int C, int group, float eps, int gate_first) {
+                                        int w_period, int C, int group, float eps, int gate_first, int gate_act) {
   __shared__ float red[33];
   const int t = blockIdx.x, g0 = blockIdx.y * group;
   const float* yr = y + static_cast<size_t>(t) * ldy + g0;
   const float* gr = gate + static_cast<size_t>(t) * ldg + g0;
   float ss = 0.f;
   for (int d = threadIdx.x; d < group; d += blockDim.x) {
-    const float u = gate_first ? yr[d] * silu_exact(gr[d]) : yr[d];
+    const float u = gate_first ? yr[d] * (gate_act ? sigmoid_f(gr[d]) : silu_exact(gr[d])) : yr[d];
     ss += u * u;
   }
   ss = block_sum(ss, red);
   const float inv = 1.f / sqrtf(ss / static_cast<float>(group) + eps);
   for (int d = threadIdx.x; d < group; d += blockDim.x) {
-    const float s = silu_exact(gr[d]);
-    const float wv = w[(g0 + d) % w_period];
+    const float s = gate_act ? sigmoid_f(gr[d]) : silu_exact(gr[d]);
+    const float wv = w ? w[(g0 + d) % w_period] : 1.f;
     const float v = gate_first ? yr[d] * s * inv * wv : yr[d] * inv * wv * s;
     st(out + static_cast<size_t>(t) * C + g0 + d, v);
   }
+}
+
+
+// x[t] += y[t] / sqrt(mean(y[t]^2) + eps) * (w_offset + w): the norm AFTER a sublayer, folded into the residual sum
+__global__ void resid_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w,
+                                         int width, float eps, float w_offset) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const float* yr = y + static_cast<size_t>(t) * width;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) ss += yr[d] * yr[d];
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / static_cast<float>(width) + eps);
+  for (int d = threadIdx.x; d < width; d += blockDim.x)
+    x[static_cast<size_t>(t) * width + d] += yr[d] * inv * (w_offset + w[d]);
+}
+
+// y[t, d] += scale * bias[d]
+__global__ void bias_rows_kernel(float* __restrict__ y, const float* __restrict__ bias, float scale, int n, size_t total) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    y[i] += scale * bias[i % n];
 }
 
 template <typename T>
@@ -83,13 +106,13 @@ static int flat_grid(size_t total) {
   return static_cast<int>(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
 }
 
-void launch_embed_f32(float* x, const void* table, const uint32_t* ids, int T, int width, int vocab, int dt,
+void launch_embed_f32(float* x, const void* table, const uint32_t* ids, int T, int width, int vocab, float scale, int dt,
                       cudaStream_t st_) {
   if (T <= 0) return;
   if (dt)
-    embed_f32_kernel<float><<<T, 256, 0, st_>>>(x, (const float*)table, ids, width, vocab);
+    embed_f32_kernel<float><<<T, 256, 0, st_>>>(x, (const float*)table, ids, width, vocab, scale);
   else
-    embed_f32_kernel<__nv_bfloat16><<<T, 256, 0, st_>>>(x, (const __nv_bfloat16*)table, ids, width, vocab);
+    embed_f32_kernel<__nv_bfloat16><<<T, 256, 0, st_>>>(x, (const __nv_bfloat16*)table, ids, width, vocab, scale);
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -104,17 +127,31 @@ void launch_resid_rmsnorm(void* out, const float* x, const float* w, int T, int 
 }
 
 void launch_gated_group_norm(void* out, const float* y, int ldy, const float* gate, int ldg, const float* w,
-                             int w_period, int T, int C, int group, float eps, int gate_first, int dt,
+                             int w_period, int T, int C, int group, float eps, int gate_first, int gate_act, int dt,
                              cudaStream_t st_) {
   if (T <= 0) return;
   const dim3 grid(T, C / group);
   const int threads = group >= 256 ? 256 : (group >= 128 ? 128 : 64);
   if (dt)
     gated_group_norm_kernel<float><<<grid, threads, 0, st_>>>((float*)out, y, ldy, gate, ldg, w, w_period, C, group,
-                                                              eps, gate_first);
+                                                              eps, gate_first, gate_act);
   else
     gated_group_norm_kernel<__nv_bfloat16><<<grid, threads, 0, st_>>>((__nv_bfloat16*)out, y, ldy, gate, ldg, w,
-                                                                      w_period, C, group, eps, gate_first);
+                                                                      w_period, C, group, eps, gate_first, gate_act);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_resid_add_rmsnorm(float* x, const float* y, const float* w, int T, int width, float eps, float w_offset,
+                              cudaStream_t st_) {
+  if (T <= 0) return;
+  resid_add_rmsnorm_kernel<<<T, 256, 0, st_>>>(x, y, w, width, eps, w_offset);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+void launch_bias_rows(float* y, const float* bias, float scale, int T, int n, cudaStream_t st_) {
+  const size_t total = static_cast<size_t>(T) * n;
+  if (total == 0) return;
+  bias_rows_kernel<<<flat_grid(total), 256, 0, st_>>>(y, bias, scale, n, total);
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -151,13 +188,20 @@ void b200_resid_rmsnorm(void* out, const float* x, const float* w, int32_t num_t
 }
 // Grouped RMS norm with a SiLU gate over fp32 rows y [T, C] (row stride ldy), gate [T, C] (row stride ldg); groups of
 // `group` consecutive channels are normalised separately; w fp32 is indexed by channel % w_period (a per-head weight
-// shared by all heads has w_period = group).  gate_first != 0: norm(y * silu(gate)) * w; else norm(y) * w * silu(gate).
+// shared by all heads has w_period = group; w NULL: no weight).  gate_first != 0: norm(y * act(gate)) * w; else
+// norm(y) * w * act(gate); act = SiLU (gate_act 0) or sigmoid (gate_act 1).
 void b200_gated_group_norm(void* out, const float* y, int32_t ldy, const float* gate, int32_t ldg, const float* w,
                            int32_t w_period, int32_t num_tokens, int32_t channels, int32_t group, float eps,
-                           int32_t gate_first, int32_t dt, int64_t stream) {
-  B200_CHECK_ARG(out && y && gate && w && group > 0 && channels % group == 0 && w_period > 0 && (dt == 0 || dt == 1),
+                           int32_t gate_first, int32_t gate_act, int32_t dt, int64_t stream) {
+  B200_CHECK_ARG(out && y && gate && group > 0 && channels % group == 0 && w_period > 0 && (dt == 0 || dt == 1),
                  "gated_group_norm: bad arguments");
-  b200::launch_gated_group_norm(out, y, ldy, gate, ldg, w, w_period, num_tokens, channels, group, eps, gate_first, dt,
-                                reinterpret_cast<cudaStream_t>(stream));
+  b200::launch_gated_group_norm(out, y, ldy, gate, ldg, w, w_period, num_tokens, channels, group, eps, gate_first,
+                                gate_act, dt, reinterpret_cast<cudaStream_t>(stream));
+}
+// x fp32 [T, width] += y / sqrt(mean(y^2) + eps) * (w_offset + w): the norm that follows a sublayer, with its residual sum.
+void b200_resid_add_rmsnorm(float* x, const float* y, const float* w, int32_t num_tokens, int32_t width, float eps,
+                            float w_offset, int64_t stream) {
+  B200_CHECK_ARG(x && y && w && width > 0, "resid_add_rmsnorm: bad arguments");
+  b200::launch_resid_add_rmsnorm(x, y, w, num_tokens, width, eps, w_offset, reinterpret_cast<cudaStream_t>(stream));
 }
 }

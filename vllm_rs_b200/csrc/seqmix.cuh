@@ -1,4 +1,5 @@
-// Shared pieces of the sequence-mixer kernels (latent attention, gated delta rule, SSD scan, routed experts)
+// Shared pieces of the sequence-mixer kernels (latent and windowed attention, gated delta rule, SSD scan, decayed
+// linear attention, routed experts)
 // of hybrid decoders whose residual stream, norms, softmax, routers and recurrent state are kept in fp32.
 //
 // Activation dtype: every buffer that FEEDS a matrix product (and the latent KV cache) is either bf16 or fp32,
@@ -67,12 +68,16 @@ __device__ __forceinline__ int seq_of_row(const uint32_t* __restrict__ cu, int n
 
 }  // namespace seqmix
 
-// ---- launchers (seq_norms.cu, latent_attn.cu, linear_recurrence.cu, moe.cu, gemm_lib.cu); dt: 0 bf16, 1 fp32
-void launch_embed_f32(float* x, const void* table, const uint32_t* ids, int T, int width, int vocab, int dt, cudaStream_t st);
+// ---- launchers (seq_norms.cu, latent_attn.cu, window_attn.cu, linear_recurrence.cu, moe.cu, gemm_lib.cu); dt: 0 bf16, 1 fp32
+void launch_embed_f32(float* x, const void* table, const uint32_t* ids, int T, int width, int vocab, float scale, int dt,
+                      cudaStream_t st);
 void launch_resid_rmsnorm(void* out, const float* x, const float* w, int T, int width, float eps, float w_offset,
                           const uint32_t* rows, int dt, cudaStream_t st);
 void launch_gated_group_norm(void* out, const float* y, int ldy, const float* gate, int ldg, const float* w, int w_period,
-                             int T, int C, int group, float eps, int gate_first, int dt, cudaStream_t st);
+                             int T, int C, int group, float eps, int gate_first, int gate_act, int dt, cudaStream_t st);
+void launch_resid_add_rmsnorm(float* x, const float* y, const float* w, int T, int width, float eps, float w_offset,
+                              cudaStream_t st);
+void launch_bias_rows(float* y, const float* bias, float scale, int T, int n, cudaStream_t st);
 void launch_cast_rows(void* out, const float* in, int ld_in, int T, int n, int dt, cudaStream_t st);
 void launch_silu_mul_f32(void* out, const float* gate_up, int T, int ff, int dt, cudaStream_t st);
 
@@ -83,6 +88,17 @@ void launch_latent_attn(void* out, const float* q_full, const void* cache, const
                         const uint32_t* ctx, const uint32_t* block_tables, int max_blocks, int num_seqs, int T, int heads,
                         int kv_rank, int rot_dim, int window, float scale, int dt, void* workspace, cudaStream_t st);
 size_t latent_attn_workspace_bytes(int T, int heads, int kv_rank, int window);
+
+void launch_window_attn_prep(const float* proj, int ld, const float* bias, const float* q_norm_w, const float* k_norm_w,
+                             const double* rot_freq, const int64_t* positions, const int64_t* slots, float* q_out,
+                             void* k_cache, void* v_cache, int T, int heads, int kv_heads, int dim, int vdim,
+                             int rot_dims, float eps, int dt, cudaStream_t st);
+void launch_window_attn(void* out, const float* q, const void* k_cache, const void* v_cache, const float* sink,
+                        const float* gate, int ld_gate, const uint32_t* cu, const uint32_t* ctx,
+                        const uint32_t* block_tables, int max_blocks, int num_seqs, int T, int heads, int kv_heads,
+                        int dim, int vdim, int window, int keep_first, float scale, float softcap, int dt,
+                        void* workspace, cudaStream_t st);
+size_t window_attn_workspace_bytes(int T, int heads, int kv_heads, int vdim, int window, int keep_first);
 
 void launch_short_conv_silu(float* out, int ldo, const float* x, int ldx, const float* taps_w, const float* bias,
                             float* state, const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs,
@@ -95,6 +111,13 @@ void launch_ssd_scan(float* out, const float* x, const float* Bm, const float* C
                      int ld_dt, const float* a_log, const float* dt_bias, const float* d_skip, float* state,
                      const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads, int groups,
                      int nstate, int vdim, cudaStream_t st);
+
+void launch_lowrank_decay(float* out, const float* low, int ld_low, const float* w2, const float* bias, float tau, int T,
+                          int C, int rank, cudaStream_t st);
+void launch_decay_attn(float* out, const float* q, const float* k, const float* v, int ld, const float* head_decay,
+                       const float* chan_decay, int ld_decay, float q_scale, float k_scale, int act, float* state,
+                       const int32_t* slots, const uint32_t* cu, const uint32_t* ctx, int num_seqs, int heads, int dim,
+                       int vdim, cudaStream_t st);
 
 void launch_moe_route(const float* logits, int T, int E, int top, float scale, int32_t* top_idx, float* top_w,
                       cudaStream_t st);
@@ -111,5 +134,9 @@ void launch_moe_combine(float* x, const float* down, const int32_t* slot_of_pair
 // reduced-precision mode for fp32 operands.  `batch` > 1: strided batches.  w_kn != 0: W is stored [K, N] (ldw >= N).
 bool gemm_f32out(const void* a, int lda, long long stride_a, const void* w, int ldw, long long stride_w, float* c, int ldc,
                  long long stride_c, int M, int N, int K, int batch, float beta, int w_kn, int dt, cudaStream_t st);
+// the same with C = alpha * A x W^T + beta * C
+bool gemm_f32out_scaled(const void* a, int lda, long long stride_a, const void* w, int ldw, long long stride_w, float* c,
+                        int ldc, long long stride_c, int M, int N, int K, int batch, float alpha, float beta, int w_kn,
+                        int dt, cudaStream_t st);
 
 }  // namespace b200

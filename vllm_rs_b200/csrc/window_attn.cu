@@ -1,0 +1,595 @@
+// Softmax attention with grouped key / value heads over paged K and V caches, for ragged steps (prompt portions and
+// decoded tokens alike), for decoders that keep queries, scores and the softmax in fp32.  Beside latent_attn.cu (one
+// shared latent row per token) and paged_attn_decode.cu / attn_prefill*.cu (fp16 / bf16 residual models).
+//
+// Caches, one row per token and layer, pages of 64 tokens (the block manager's blocks):
+//   k_cache [num_blocks, 64, kv_heads, dim]    v_cache [num_blocks, 64, kv_heads, vdim]    (bf16 or fp32)
+// Query head h reads key / value head h / (heads / kv_heads).  Options, each a parameter:
+//   * sliding window that keeps the first tokens: position i sees j <= i with i - j < window or j < keep_first
+//     (window <= 0: every j <= i); kept tokens keep their own positions
+//   * capped scores: s <- cap * tanh(s / cap)  (cap <= 0: off), applied after the scale
+//   * a per-head sink logit that joins the softmax denominator without a key or value (NULL: none); a logit of 0 is
+//     "one added to the denominator"
+//   * a per-head output gate: the head's output is multiplied by sigmoid(gate[t, h]) (NULL: none)
+//
+// window_attn_prep_kernel: from the fused projection row [q (heads x dim) | k (kv_heads x dim) | v (kv_heads x vdim) | ...]
+// (fp32) it adds the projection biases, RMS-norms q and k over their WHOLE projection (all heads at once, weights of
+// that size; NULL: no norm), rotates the first rot_dims entries of every q and k head as interleaved pairs (2i, 2i+1)
+// by the angle position * freq[i] (angles in double), writes the K and V rows at the token's slot and the query in fp32.
+//
+// Two attention kernels: an fp32 FMA form (any sizes, both dtypes; the rows of small steps split their keys over several
+// blocks and merge) and a bf16 tensor-core form for steps of many rows.
+#include "../../include/b200_vllm.h"
+#include <algorithm>
+#include <cstdlib>
+
+#include "seqmix.cuh"
+
+namespace b200 {
+using namespace seqmix;
+
+template <typename T>
+__global__ void window_attn_prep_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias,
+                                        const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
+                                        const double* __restrict__ rot_freq, const int64_t* __restrict__ positions,
+                                        const int64_t* __restrict__ slots, float* __restrict__ q_out,
+                                        T* __restrict__ k_cache, T* __restrict__ v_cache, int heads, int kv_heads,
+                                        int dim, int vdim, int rot_dims, float eps) {
+  extern __shared__ float sm[];          // cos[rot_dims/2] | sin[rot_dims/2] | red[33]
+  const int half = rot_dims / 2;
+  float* cs = sm;
+  float* sn = sm + half;
+  float* red = sm + 2 * half;
+  const int t = blockIdx.x;
+  const int nq = heads * dim, nk = kv_heads * dim, nv = kv_heads * vdim;
+  const float* qr = proj + static_cast<size_t>(t) * ld;
+  const float* kr = qr + nq;
+  const float* vr = kr + nk;
+  const float* bq = bias;
+  const float* bk = bias ? bias + nq : nullptr;
+  const float* bv = bias ? bias + nq + nk : nullptr;
+  const double pos = static_cast<double>(positions[t]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double s, c;
+    sincos(pos * rot_freq[i], &s, &c);
+    cs[i] = static_cast<float>(c);
+    sn[i] = static_cast<float>(s);
+  }
+  float inv_q = 1.f, inv_k = 1.f;
+  if (q_norm_w) {
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < nq; d += blockDim.x) {
+      const float v = qr[d] + (bq ? bq[d] : 0.f);
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    inv_q = 1.f / sqrtf(ss / static_cast<float>(nq) + eps);
+  }
+  if (k_norm_w) {
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < nk; d += blockDim.x) {
+      const float v = kr[d] + (bk ? bk[d] : 0.f);
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    inv_k = 1.f / sqrtf(ss / static_cast<float>(nk) + eps);
+  }
+  __syncthreads();                       // the cos / sin table is complete
+  // one (possibly rotated) entry of a projection whose heads are `dim` wide
+  auto entry = [&](const float* raw, const float* b, const float* w, float inv, int e) {
+    auto plain = [&](int i) { return (raw[i] + (b ? b[i] : 0.f)) * inv * (w ? w[i] : 1.f); };
+    const int d = e % dim;
+    if (d >= rot_dims) return plain(e);
+    const int i = d >> 1, e0 = e - (d & 1);
+    const float u = plain(e0), v = plain(e0 + 1);
+    return (d & 1) ? v * cs[i] + u * sn[i] : u * cs[i] - v * sn[i];
+  };
+  for (int e = threadIdx.x; e < nq; e += blockDim.x)
+    q_out[static_cast<size_t>(t) * nq + e] = entry(qr, bq, q_norm_w, inv_q, e);
+  const int64_t slot = slots[t];
+  if (slot >= 0) {
+    for (int e = threadIdx.x; e < nk; e += blockDim.x)
+      st(k_cache + static_cast<size_t>(slot) * nk + e, entry(kr, bk, k_norm_w, inv_k, e));
+    for (int e = threadIdx.x; e < nv; e += blockDim.x)
+      st(v_cache + static_cast<size_t>(slot) * nv + e, vr[e] + (bv ? bv[e] : 0.f));
+  }
+}
+
+// The keys that position `pos` sees, as one run of indices 0 .. count-1: first the kept tokens that have left the
+// window, then the window itself.
+struct Visible {
+  int n_first, lo, count;
+  __device__ __forceinline__ Visible(int pos, int window, int keep_first) {
+    lo = window > 0 ? max(0, pos - window + 1) : 0;
+    n_first = min(max(keep_first, 0), lo);
+    count = n_first + (pos - lo + 1);
+  }
+  __device__ __forceinline__ int key(int idx) const { return idx < n_first ? idx : lo + (idx - n_first); }
+};
+
+__device__ __forceinline__ float cap_score(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+
+// grid = (token rows, kv heads, key splits); a block's warps each own one query head of the group at a time.  The K and
+// V rows of a tile of visible keys are staged once in shared memory (fp32) and used by every head of the group.
+template <typename T>
+__global__ void window_attn_kernel(T* __restrict__ out, const float* __restrict__ q, const T* __restrict__ k_cache,
+                                   const T* __restrict__ v_cache, const float* __restrict__ sink,
+                                   const float* __restrict__ gate, int ld_gate, const uint32_t* __restrict__ cu,
+                                   const uint32_t* __restrict__ ctx, const uint32_t* __restrict__ block_tables,
+                                   int max_blocks, int num_seqs, int heads, int kv_heads, int dim, int vdim, int window,
+                                   int keep_first, float scale, float softcap, int key_tile, int nsplit,
+                                   float* __restrict__ part_o, float* __restrict__ part_ml) {
+  extern __shared__ float sm[];
+  const int Dp = dim | 1;                               // odd row pitch: a lane per key reads conflict-free
+  const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* ks = sm;                                       // [key_tile][Dp]
+  float* vs = ks + static_cast<size_t>(key_tile) * Dp;  // [key_tile][vdim]
+  float* qs = vs + static_cast<size_t>(key_tile) * vdim;   // [nw][dim]
+  float* os = qs + static_cast<size_t>(nw) * dim;       // [nw][vdim]
+  const int t = blockIdx.x, g = blockIdx.y;
+  const int b = seq_of_row(cu, num_seqs, t);
+  const int qlen = static_cast<int>(cu[b + 1] - cu[b]);
+  const int pos = static_cast<int>(ctx[b]) - qlen + (t - static_cast<int>(cu[b]));
+  const Visible vis(pos, window, keep_first);
+  const int per_group = heads / kv_heads;
+  const uint32_t* bt = block_tables + static_cast<size_t>(b) * max_blocks;
+  const int ntiles = (vis.count + key_tile - 1) / key_tile;
+  const int per = (ntiles + nsplit - 1) / nsplit;
+  const int first = static_cast<int>(blockIdx.z) * per * key_tile;
+  const int last = min(vis.count, first + per * key_tile);            // exclusive
+  for (int h0 = 0; h0 < per_group; h0 += nw) {                         // groups wider than the block take several rounds
+    const int hg = h0 + warp;
+    const bool live = hg < per_group;
+    const int h = g * per_group + hg;
+    __syncthreads();
+    if (live) {
+      const float* qh = q + (static_cast<size_t>(t) * heads + h) * dim;
+      for (int d = lane; d < dim; d += 32) qs[warp * dim + d] = qh[d];
+      for (int d = lane; d < vdim; d += 32) os[warp * vdim + d] = 0.f;
+    }
+    float m = -1e30f, l = 0.f;
+    if (live && sink && nsplit == 1) {        // split runs add the sink when the parts are merged
+      m = sink[h];
+      l = 1.f;
+    }
+    for (int i0 = first; i0 < last; i0 += key_tile) {
+      const int nk = min(key_tile, last - i0);
+      __syncthreads();
+      for (int e = threadIdx.x; e < nk * dim; e += blockDim.x) {
+        const int k = e / dim, d = e % dim, j = vis.key(i0 + k);
+        const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
+        ks[k * Dp + d] = ld(k_cache + (slot * kv_heads + g) * dim + d);
+      }
+      for (int e = threadIdx.x; e < nk * vdim; e += blockDim.x) {
+        const int k = e / vdim, d = e % vdim, j = vis.key(i0 + k);
+        const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
+        vs[k * vdim + d] = ld(v_cache + (slot * kv_heads + g) * vdim + d);
+      }
+      __syncthreads();
+      if (!live) continue;
+      for (int k0 = 0; k0 < nk; k0 += 32) {
+        const int k = k0 + lane;
+        float s = -1e30f;
+        if (k < nk) {
+          float acc = 0.f;
+          const float* kr = ks + k * Dp;
+          const float* qw = qs + warp * dim;
+          for (int d = 0; d < dim; ++d) acc += qw[d] * kr[d];
+          s = cap_score(acc * scale, softcap);
+        }
+        const float mt = lanes_max(s);
+        const float mn = fmaxf(m, mt);
+        const float alpha = expf(m - mn);
+        const float p = k < nk ? expf(s - mn) : 0.f;
+        l = l * alpha + lanes_sum(p);
+        m = mn;
+        const int cnt = min(32, nk - k0);
+        for (int d0 = 0; d0 < vdim; d0 += 32) {          // every lane takes part in the shuffles
+          const int d = d0 + lane;
+          const bool ok = d < vdim;
+          float acc = ok ? os[warp * vdim + d] * alpha : 0.f;
+          for (int kk = 0; kk < cnt; ++kk) {
+            const float pk = __shfl_sync(0xffffffffu, p, kk);
+            if (ok) acc += pk * vs[(k0 + kk) * vdim + d];
+          }
+          if (ok) os[warp * vdim + d] = acc;
+        }
+      }
+    }
+    if (live && nsplit == 1) {
+      float inv = l > 0.f ? 1.f / l : 0.f;
+      if (gate) inv *= sigmoid_f(gate[static_cast<size_t>(t) * ld_gate + h]);
+      T* o = out + (static_cast<size_t>(t) * heads + h) * vdim;
+      for (int d = lane; d < vdim; d += 32) st(o + d, os[warp * vdim + d] * inv);
+    } else if (live) {
+      const size_t pi = (static_cast<size_t>(t) * heads + h) * nsplit + blockIdx.z;
+      for (int d = lane; d < vdim; d += 32) part_o[pi * vdim + d] = os[warp * vdim + d];
+      if (lane == 0) {
+        part_ml[pi * 2] = m;
+        part_ml[pi * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// one block per (token, head): the parts of a split run and the sink meet in one softmax; the gate is applied here
+template <typename T>
+__global__ void window_attn_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o,
+                                         const float* __restrict__ part_ml, const float* __restrict__ sink,
+                                         const float* __restrict__ gate, int ld_gate, int heads, int vdim, int nsplit) {
+  const size_t th = blockIdx.x;
+  const int h = static_cast<int>(th % heads);
+  const size_t t = th / heads;
+  const float* ml = part_ml + th * nsplit * 2;
+  float m = sink ? sink[h] : -1e30f;
+  for (int z = 0; z < nsplit; ++z) m = fmaxf(m, ml[2 * z]);
+  float l = sink ? expf(sink[h] - m) : 0.f;
+  for (int z = 0; z < nsplit; ++z) l += ml[2 * z + 1] * expf(ml[2 * z] - m);
+  float inv = l > 0.f ? 1.f / l : 0.f;
+  if (gate) inv *= sigmoid_f(gate[t * ld_gate + h]);
+  for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < nsplit; ++z) acc += part_o[(th * nsplit + z) * vdim + d] * expf(ml[2 * z] - m);
+    st(out + th * vdim + d, acc * inv);
+  }
+}
+
+void launch_window_attn_prep(const float* proj, int ld, const float* bias, const float* q_norm_w, const float* k_norm_w,
+                             const double* rot_freq, const int64_t* positions, const int64_t* slots, float* q_out,
+                             void* k_cache, void* v_cache, int T, int heads, int kv_heads, int dim, int vdim,
+                             int rot_dims, float eps, int dt, cudaStream_t st_) {
+  if (T <= 0) return;
+  const size_t smem = (static_cast<size_t>(rot_dims) + 40) * 4;
+  if (dt)
+    window_attn_prep_kernel<float><<<T, 256, smem, st_>>>(proj, ld, bias, q_norm_w, k_norm_w, rot_freq, positions, slots,
+                                                          q_out, (float*)k_cache, (float*)v_cache, heads, kv_heads, dim,
+                                                          vdim, rot_dims, eps);
+  else
+    window_attn_prep_kernel<__nv_bfloat16><<<T, 256, smem, st_>>>(proj, ld, bias, q_norm_w, k_norm_w, rot_freq, positions,
+                                                                  slots, q_out, (__nv_bfloat16*)k_cache,
+                                                                  (__nv_bfloat16*)v_cache, heads, kv_heads, dim, vdim,
+                                                                  rot_dims, eps);
+  B200_CUDA_LAUNCH_CHECK();
+}
+
+// ---- bf16 tensor-core form for steps of many rows (prompt portions).  Block = 4 warps = one query head x 16
+// consecutive token rows of ONE sequence.  Per tile of 64 visible-key candidates: every warp computes the scores of 16
+// keys (S = Q K^T, mma.sync m16n8k16 bf16 -> fp32, Q and K from shared memory), the fp32 scores meet in shared memory,
+// every warp runs the same fp32 online softmax over all 64 (cap, window / kept-first / causal mask per element, sink as
+// the initial denominator) and multiplies P (bf16) with ITS quarter of the value columns (V fragments by
+// ldmatrix.trans).  Tiles are 64-aligned runs of positions: first those that hold kept tokens, then those from the
+// window's start of the block's first row to its last row; a tile is visited once.
+constexpr int WQ = 16, WKT = 64;
+__device__ __forceinline__ void wmma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t wpack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// NT = n-tiles (8 value columns each) per warp = vdim / 32
+template <int NT>
+__global__ void __launch_bounds__(128)
+window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ q,
+                       const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                       const float* __restrict__ sink, const float* __restrict__ gate, int ld_gate,
+                       const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
+                       const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_heads,
+                       int dim, int vdim, int window, int keep_first, float scale, float softcap) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int P = dim + 8, PV = vdim + 8;                   // row pitches in bf16 elements (16-byte multiples)
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [WKT][P]
+  __nv_bfloat16* Vs = Ks + static_cast<size_t>(WKT) * P;                    // [WKT][PV]
+  __nv_bfloat16* Qs = Vs + static_cast<size_t>(WKT) * PV;                   // [WQ][P]
+  float* Ss = reinterpret_cast<float*>(Qs + static_cast<size_t>(WQ) * P);   // [WQ][WKT + 1]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  // 16 token rows of one sequence (tiles never straddle sequences)
+  int b = -1, row0 = 0, nrows = 0;
+  {
+    int acc = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+      const int n = static_cast<int>(cu[s + 1] - cu[s]), tiles = (n + WQ - 1) / WQ;
+      if (static_cast<int>(blockIdx.x) < acc + tiles) {
+        const int k = blockIdx.x - acc;
+        b = s;
+        row0 = cu[s] + k * WQ;
+        nrows = min(WQ, n - k * WQ);
+        break;
+      }
+      acc += tiles;
+    }
+    if (b < 0) return;
+  }
+  const int h = blockIdx.y, kvh = h / (heads / kv_heads);
+  const int pos0 = static_cast<int>(ctx[b]) - static_cast<int>(cu[b + 1] - cu[b]) + (row0 - static_cast<int>(cu[b]));
+  const int pos_last = pos0 + nrows - 1;
+  const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;        // first key of the window of the first row
+  for (int e = threadIdx.x; e < WQ * dim; e += blockDim.x) {
+    const int r = e / dim, d = e % dim;
+    const float v = r < nrows ? q[(static_cast<size_t>(row0 + r) * heads + h) * dim + d] : 0.f;
+    Qs[r * P + d] = __float2bfloat16_rn(v);
+  }
+  float m[2], l[2];
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    m[rr] = sink ? sink[h] : -1e30f;
+    l[rr] = sink ? 1.f : 0.f;
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  const uint32_t* bt = block_tables + static_cast<size_t>(b) * max_blocks;
+  const int rowp[2] = {pos0 + g, pos0 + g + 8};           // positions of this lane's two rows
+  // 64-aligned tiles: [0, kept_end) holds the kept tokens outside the window, [win_begin, pos_last] the window
+  const int win_begin = (key_lo / WKT) * WKT;
+  const int kept_end = min(win_begin, ((min(max(keep_first, 0), key_lo) + WKT - 1) / WKT) * WKT);
+  for (int j0 = 0; j0 <= pos_last; j0 += WKT) {
+    if (j0 >= kept_end && j0 < win_begin) j0 = win_begin;
+    __syncthreads();
+    const int kvec = dim / 8, vvec = vdim / 8;
+    for (int e = threadIdx.x; e < WKT * kvec; e += blockDim.x) {
+      const int k = e / kvec, d = (e % kvec) * 8, j = j0 + k;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j <= pos_last) {
+        const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
+        v = *reinterpret_cast<const uint4*>(k_cache + (slot * kv_heads + kvh) * dim + d);
+      }
+      *reinterpret_cast<uint4*>(Ks + static_cast<size_t>(k) * P + d) = v;
+    }
+    for (int e = threadIdx.x; e < WKT * vvec; e += blockDim.x) {
+      const int k = e / vvec, d = (e % vvec) * 8, j = j0 + k;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j <= pos_last) {
+        const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
+        v = *reinterpret_cast<const uint4*>(v_cache + (slot * kv_heads + kvh) * vdim + d);
+      }
+      *reinterpret_cast<uint4*>(Vs + static_cast<size_t>(k) * PV + d) = v;
+    }
+    __syncthreads();
+    // scores of keys [16 warp, 16 warp + 16)
+    float sc[2][4] = {};
+    for (int kk = 0; kk < dim; kk += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(Qs + g * P + kk + 2 * tq);
+      a[1] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * P + kk + 2 * tq);
+      a[2] = *reinterpret_cast<const uint32_t*>(Qs + g * P + kk + 2 * tq + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(Qs + (g + 8) * P + kk + 2 * tq + 8);
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        const __nv_bfloat16* kr = Ks + static_cast<size_t>(warp * 16 + nb * 8 + g) * P + kk + 2 * tq;
+        wmma_bf16_16816(sc[nb], a, *reinterpret_cast<const uint32_t*>(kr), *reinterpret_cast<const uint32_t*>(kr + 8));
+      }
+    }
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        const int r = g + (f >> 1) * 8, kcol = warp * 16 + nb * 8 + 2 * tq + (f & 1);
+        Ss[r * (WKT + 1) + kcol] = cap_score(sc[nb][f] * scale, softcap);
+      }
+    __syncthreads();
+    // the same online softmax in every warp; this lane's P entries are exactly its A fragments
+    float p[2][16];
+    float mx[2] = {-1e30f, -1e30f};
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int r = g + rr * 8;
+      const int lo = window > 0 ? max(0, rowp[rr] - window + 1) : 0;
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int kcol = ks * 16 + 2 * tq + (c & 1) + (c >> 1) * 8, j = j0 + kcol;
+          const bool ok = r < nrows && j <= rowp[rr] && (j >= lo || j < keep_first);
+          const float v = ok ? Ss[r * (WKT + 1) + kcol] : -1e30f;
+          p[rr][ks * 4 + c] = v;
+          mx[rr] = fmaxf(mx[rr], v);
+        }
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+    }
+    float alpha[2];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const float mn = fmaxf(m[rr], mx[rr]);
+      alpha[rr] = expf(m[rr] - mn);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float e = p[rr][i] > -1e29f ? expf(p[rr][i] - mn) : 0.f;
+        p[rr][i] = e;
+        sum += e;
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l[rr] = l[rr] * alpha[rr] + sum;
+      m[rr] = mn;
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+    }
+    // O += P V over this warp's value columns [warp * NT * 8, +NT * 8)
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      uint32_t a[4];
+      a[0] = wpack_bf16(p[0][ks * 4 + 0], p[0][ks * 4 + 1]);
+      a[1] = wpack_bf16(p[1][ks * 4 + 0], p[1][ks * 4 + 1]);
+      a[2] = wpack_bf16(p[0][ks * 4 + 2], p[0][ks * 4 + 3]);
+      a[3] = wpack_bf16(p[1][ks * 4 + 2], p[1][ks * 4 + 3]);
+#pragma unroll
+      for (int n = 0; n < NT; n += 2) {
+        // four 8 x 8 blocks: (keys 0-7 | 8-15 of the step) x (columns d0 .. d0+7 | d0+8 .. d0+15), transposed on load
+        const int d0 = (warp * NT + n) * 8;
+        const __nv_bfloat16* src = Vs + static_cast<size_t>(ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * PV + d0 + (lane >> 4) * 8;
+        uint32_t r0, r1, r2, r3;
+        const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(src));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+        wmma_bf16_16816(o[n], a, r0, r1);
+        if (n + 1 < NT) wmma_bf16_16816(o[n + 1], a, r2, r3);
+      }
+    }
+  }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int r = g + rr * 8;
+    if (r >= nrows) continue;
+    float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
+    if (gate) inv *= sigmoid_f(gate[static_cast<size_t>(row0 + r) * ld_gate + h]);
+    const size_t orow = static_cast<size_t>(row0 + r) * heads + h;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const int d = (warp * NT + n) * 8 + 2 * tq;
+      __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
+      *reinterpret_cast<__nv_bfloat162*>(out + orow * vdim + d) = v;
+    }
+  }
+}
+
+static bool window_mma_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200_WINDOW_MMA");       // 0: the FMA kernel for every step (A/B arm)
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+static size_t window_mma_smem(int dim, int vdim) {
+  return static_cast<size_t>(WKT + WQ) * (dim + 8) * 2 + static_cast<size_t>(WKT) * (vdim + 8) * 2 +
+         static_cast<size_t>(WQ) * (WKT + 1) * 4;
+}
+static bool window_mma_shape_ok(int dim, int vdim) {
+  return dim % 16 == 0 && vdim % 32 == 0 && vdim <= 256 && window_mma_smem(dim, vdim) <= 200 * 1024;
+}
+
+static int window_attn_warps(int heads, int kv_heads) {
+  const int pg = heads / kv_heads;
+  return pg >= 8 ? 8 : (pg >= 4 ? 4 : (pg >= 2 ? 2 : 1));
+}
+int window_attn_splits(int T, int heads, int kv_heads, int window, int keep_first) {
+  (void)heads;
+  const int blocks = T * kv_heads;
+  int n = (2 * sm_count() + blocks - 1) / blocks;           // aim at two blocks per SM
+  if (window > 0) n = std::min(n, (window + std::max(keep_first, 0) + 31) / 32);
+  return std::max(1, std::min(n, 16));
+}
+size_t window_attn_workspace_bytes(int T, int heads, int kv_heads, int vdim, int window, int keep_first) {
+  const int n = window_attn_splits(T, heads, kv_heads, window, keep_first);
+  return n == 1 ? 0 : static_cast<size_t>(T) * heads * n * (vdim + 2) * 4;
+}
+
+void launch_window_attn(void* out, const float* q, const void* k_cache, const void* v_cache, const float* sink,
+                        const float* gate, int ld_gate, const uint32_t* cu, const uint32_t* ctx,
+                        const uint32_t* block_tables, int max_blocks, int num_seqs, int T, int heads, int kv_heads,
+                        int dim, int vdim, int window, int keep_first, float scale, float softcap, int dt,
+                        void* workspace, cudaStream_t st_) {
+  if (T <= 0) return;
+  // steps of many rows in bf16: the tensor-core kernel (small steps keep the split form below)
+  if (!dt && T > 2 * sm_count() / 4 && window_mma_enabled() && window_mma_shape_ok(dim, vdim)) {
+    const size_t smem = window_mma_smem(dim, vdim);
+    const dim3 grid((T + WQ - 1) / WQ + num_seqs, heads, 1);
+#define B200_WMMA(NT)                                                                                             \
+  {                                                                                                                \
+    auto kern = window_attn_mma_kernel<NT>;                                                                        \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));               \
+    kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,                          \
+                                   (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,      \
+                                   max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,    \
+                                   softcap);                                                                       \
+  }
+    bool done = true;
+    switch (vdim / 32) {
+      case 1: B200_WMMA(1) break;
+      case 2: B200_WMMA(2) break;
+      case 3: B200_WMMA(3) break;
+      case 4: B200_WMMA(4) break;
+      case 6: B200_WMMA(6) break;
+      case 8: B200_WMMA(8) break;
+      default: done = false;
+    }
+#undef B200_WMMA
+    if (done) {
+      B200_CUDA_LAUNCH_CHECK();
+      return;
+    }
+  }
+  const int Dp = dim | 1;
+  const int nw = window_attn_warps(heads, kv_heads);
+  int key_tile = 32;
+  auto bytes = [&](int kt) {
+    return (static_cast<size_t>(kt) * (Dp + vdim) + static_cast<size_t>(nw) * (dim + vdim)) * 4;
+  };
+  while (key_tile > 1 && bytes(key_tile) > 200 * 1024) key_tile >>= 1;
+  const size_t smem = bytes(key_tile);
+  if (smem > 220 * 1024) {
+    set_error(1, "window_attn: dim + vdim too large for the shared-memory tile");
+    return;
+  }
+  // few token rows (decoding): the keys of a row are split over several blocks and merged afterwards
+  const int nsplit = workspace ? window_attn_splits(T, heads, kv_heads, window, keep_first) : 1;
+  float* part_o = reinterpret_cast<float*>(workspace);
+  float* part_ml = part_o ? part_o + static_cast<size_t>(T) * heads * nsplit * vdim : nullptr;
+  const dim3 grid(T, kv_heads, nsplit);
+  if (dt) {
+    auto kern = window_attn_kernel<float>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, nw * 32, smem, st_>>>((float*)out, q, (const float*)k_cache, (const float*)v_cache, sink, gate, ld_gate,
+                                       cu, ctx, block_tables, max_blocks, num_seqs, heads, kv_heads, dim, vdim, window,
+                                       keep_first, scale, softcap, key_tile, nsplit, part_o, part_ml);
+  } else {
+    auto kern = window_attn_kernel<__nv_bfloat16>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, nw * 32, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,
+                                       (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,
+                                       max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,
+                                       softcap, key_tile, nsplit, part_o, part_ml);
+  }
+  B200_CUDA_LAUNCH_CHECK();
+  if (nsplit > 1) {
+    const int th = vdim >= 256 ? 256 : (vdim >= 128 ? 128 : 64);
+    if (dt)
+      window_attn_merge_kernel<float><<<T * heads, th, 0, st_>>>((float*)out, part_o, part_ml, sink, gate, ld_gate,
+                                                                 heads, vdim, nsplit);
+    else
+      window_attn_merge_kernel<__nv_bfloat16><<<T * heads, th, 0, st_>>>((__nv_bfloat16*)out, part_o, part_ml, sink,
+                                                                         gate, ld_gate, heads, vdim, nsplit);
+    B200_CUDA_LAUNCH_CHECK();
+  }
+}
+
+}  // namespace b200
+
+extern "C" {
+void b200_window_attn_prep(const float* proj, int32_t ld, const float* bias, const float* q_norm_w,
+                           const float* k_norm_w, const double* rot_freq, const int64_t* positions,
+                           const int64_t* slot_mapping, float* q_out, void* k_cache, void* v_cache, int32_t num_tokens,
+                           int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t rot_dims, float eps,
+                           int32_t dt, int64_t stream) {
+  B200_CHECK_ARG(proj && positions && slot_mapping && q_out && k_cache && v_cache && heads > 0 && kv_heads > 0 &&
+                     heads % kv_heads == 0 && dim > 0 && vdim > 0 && rot_dims >= 0 && rot_dims <= dim &&
+                     rot_dims % 2 == 0 && (rot_dims == 0 || rot_freq) && (dt == 0 || dt == 1),
+                 "window_attn_prep: bad arguments");
+  b200::launch_window_attn_prep(proj, ld, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, q_out, k_cache,
+                                v_cache, num_tokens, heads, kv_heads, dim, vdim, rot_dims, eps, dt,
+                                reinterpret_cast<cudaStream_t>(stream));
+}
+void b200_window_attn(void* out, const float* q, const void* k_cache, const void* v_cache, const float* sink,
+                      const float* gate, int32_t ld_gate, const uint32_t* cu_seqlens_q, const uint32_t* context_lens,
+                      const uint32_t* block_tables, int32_t max_blocks_per_seq, int32_t num_seqs, int32_t num_tokens,
+                      int32_t heads, int32_t kv_heads, int32_t dim, int32_t vdim, int32_t window, int32_t keep_first,
+                      float scale, float softcap, int32_t dt, void* workspace, int64_t stream) {
+  B200_CHECK_ARG(out && q && k_cache && v_cache && cu_seqlens_q && context_lens && block_tables && num_seqs > 0 &&
+                     heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && (dt == 0 || dt == 1),
+                 "window_attn: bad arguments");
+  b200::launch_window_attn(out, q, k_cache, v_cache, sink, gate, ld_gate, cu_seqlens_q, context_lens, block_tables,
+                           max_blocks_per_seq, num_seqs, num_tokens, heads, kv_heads, dim, vdim, window, keep_first,
+                           scale, softcap, dt, workspace, reinterpret_cast<cudaStream_t>(stream));
+}
+int64_t b200_window_attn_workspace_bytes(int32_t num_tokens, int32_t heads, int32_t kv_heads, int32_t vdim,
+                                         int32_t window, int32_t keep_first) {
+  return static_cast<int64_t>(b200::window_attn_workspace_bytes(num_tokens, heads, kv_heads, vdim, window, keep_first));
+}
+}

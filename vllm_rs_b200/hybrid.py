@@ -1,9 +1,11 @@
 """Runner of hybrid decoders with an fp32 residual stream over the C++ launch plan (b200_hybrid_*,
 csrc/host/hybrid_runner.cpp): the sibling of engine.ModelRunner for models whose layers choose between latent
-attention, the gated delta rule and the SSD scan, with a routed mixture of experts beside them.
+attention, windowed softmax attention, the gated delta rule, the SSD scan and decayed linear attention (one mixer, or
+two side by side), with a routed mixture of experts or a dense gated feed-forward, in a parallel or a sandwich
+(norm before and after each sublayer) layout.
 
 This module holds no model arithmetic.  It allocates what the C side borrows -- the paged latent caches, the
-slot-indexed recurrent state pools, the workspace, pinned staging -- describes the layers to it, and moves a step's
+paged K / V caches, the slot-indexed recurrent state pools, the workspace, pinned staging -- describes the layers to it, and moves a step's
 metadata and results.  A model file (vllm_rs_b200/models/*.py) turns a checkpoint into `LayerSpec`s.
 """
 from __future__ import annotations
@@ -17,7 +19,8 @@ import torch
 from . import _lib
 from ._lib import HybridConfig, HybridLayer
 
-MIXER_LATENT_ATTN, MIXER_DELTA_RULE, MIXER_SSD = 0, 1, 2
+MIXER_LATENT_ATTN, MIXER_DELTA_RULE, MIXER_SSD, MIXER_WINDOW_ATTN, MIXER_DECAY_ATTN = 0, 1, 2, 3, 4
+LAYOUT_PARALLEL, LAYOUT_SANDWICH = 0, 1
 PAGE = 64
 
 
@@ -28,11 +31,12 @@ class LayerSpec:
     mixer: int
     dims: dict
     tensors: dict = field(default_factory=dict)
+    side: "LayerSpec | None" = None      # a second mixer beside the first (reads the same norm; outputs are summed)
 
 
 class HybridRunner:
     def __init__(self, *, width, vocab, layers: list[LayerSpec], embed, final_norm, lm_head, norm_eps,
-                 norm_weight_offset=0.0, dtype=torch.bfloat16, num_blocks, max_blocks_per_seq, max_seqs, max_tokens,
+                 norm_weight_offset=0.0, embed_scale=1.0, dtype=torch.bfloat16, num_blocks, max_blocks_per_seq, max_seqs, max_tokens,
                  num_state_slots, device="cuda", layer_trace=False):
         if dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("hybrid decoders run with bfloat16 or float32 operands")
@@ -42,18 +46,27 @@ class HybridRunner:
         self.cfg = HybridConfig(width=width, vocab=vocab, num_layers=len(layers), dt=int(dtype == torch.float32),
                                 block_size=PAGE, num_blocks=num_blocks, max_blocks_per_seq=max_blocks_per_seq,
                                 max_seqs=max_seqs, max_tokens=max_tokens, num_state_slots=num_state_slots,
-                                norm_eps=norm_eps, norm_weight_offset=norm_weight_offset)
+                                norm_eps=norm_eps, norm_weight_offset=norm_weight_offset, embed_scale=embed_scale)
         self._h = self._l.b200_hybrid_new(C.byref(self.cfg))
         _lib.check()
         self._keep = [embed, final_norm, lm_head]
-        self.kv_cache, self.conv_state, self.rec_state = {}, {}, {}
+        self.kv_cache, self.v_cache, self.conv_state, self.rec_state = {}, {}, {}, {}
         f32 = dict(dtype=torch.float32, device=self.device)
-        for i, spec in enumerate(layers):
+
+        def describe(key, spec):
+            """The C description of one mixer; allocates the caches / state pools it needs under `key`."""
             d, t = spec.dims, dict(spec.tensors)
             if spec.mixer == MIXER_LATENT_ATTN:
-                self.kv_cache[i] = torch.zeros(num_blocks, PAGE, d["kv_rank"] + d["rot_dim"], dtype=dtype,
-                                               device=self.device)
-                t["kv_cache"] = self.kv_cache[i]
+                self.kv_cache[key] = torch.zeros(num_blocks, PAGE, d["kv_rank"] + d["rot_dim"], dtype=dtype,
+                                                 device=self.device)
+                t["kv_cache"] = self.kv_cache[key]
+            elif spec.mixer == MIXER_WINDOW_ATTN:
+                self.kv_cache[key] = torch.zeros(num_blocks, PAGE, d["kv_heads"], d["dim"], dtype=dtype, device=self.device)
+                self.v_cache[key] = torch.zeros(num_blocks, PAGE, d["kv_heads"], d["vdim"], dtype=dtype, device=self.device)
+                t["kv_cache"], t["v_cache"] = self.kv_cache[key], self.v_cache[key]
+            elif spec.mixer == MIXER_DECAY_ATTN:
+                self.rec_state[key] = torch.zeros(num_state_slots, d["heads"], d["dim"], d["vdim"], **f32)
+                t["rec_state"] = self.rec_state[key]
             else:
                 taps = d["conv_taps"]
                 if spec.mixer == MIXER_DELTA_RULE:
@@ -62,19 +75,25 @@ class HybridRunner:
                 else:
                     nconv = d["heads"] * d["vdim"] + 2 * d["kv_heads"] * d["state"]
                     rows = d["state"]
-                self.conv_state[i] = torch.zeros(num_state_slots, max(taps - 1, 1), nconv, **f32)
-                self.rec_state[i] = torch.zeros(num_state_slots, d["heads"], rows, d["vdim"], **f32)
-                t["conv_state"], t["rec_state"] = self.conv_state[i], self.rec_state[i]
+                self.conv_state[key] = torch.zeros(num_state_slots, max(taps - 1, 1), nconv, **f32)
+                self.rec_state[key] = torch.zeros(num_state_slots, d["heads"], rows, d["vdim"], **f32)
+                t["conv_state"], t["rec_state"] = self.conv_state[key], self.rec_state[key]
             lw = HybridLayer(mixer=spec.mixer, **d)
             for name, ten in t.items():
                 if ten is None:
                     continue
                 if not ten.is_cuda or not ten.is_contiguous():
-                    raise ValueError(f"layer {i}: tensor {name} must be a contiguous device tensor")
+                    raise ValueError(f"layer {key}: tensor {name} must be a contiguous device tensor")
                 setattr(lw, name, ten.data_ptr())
             self._keep.append(t)
-            self._l.b200_hybrid_set_layer(self._h, i, C.byref(lw))
+            return lw
+
+        for i, spec in enumerate(layers):
+            self._l.b200_hybrid_set_layer(self._h, i, C.byref(describe(i, spec)))
             _lib.check()
+            if spec.side is not None:
+                self._l.b200_hybrid_set_layer_side(self._h, i, C.byref(describe((i, "side"), spec.side)))
+                _lib.check()
         self._l.b200_hybrid_set_globals(self._h, embed.data_ptr(), final_norm.data_ptr(), lm_head.data_ptr())
         nbytes = self._l.b200_hybrid_workspace_bytes(self._h)
         self.workspace = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)

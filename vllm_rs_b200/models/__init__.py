@@ -28,13 +28,17 @@ def architecture_of(cfg: dict) -> str:
     return name
 
 
+# architectures served by hybrid.HybridRunner (the `hybrid` build target is all they need)
+HYBRID_ARCHITECTURES = ("Fidasun", "Zalalix")
+
+
 def registered() -> list[str]:
     _load_builtin()
     return sorted(_REGISTRY)
 
 
 def _load_builtin():
-    from . import fidasun, llama  # noqa: F401  (importing registers them)
+    from . import fidasun, llama, zalalix  # noqa: F401  (importing registers them)
 
 
 def build_runner(cfg: dict, tensors: dict, **kw):

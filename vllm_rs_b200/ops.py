@@ -327,13 +327,15 @@ def resid_rmsnorm(x, w, eps, w_offset=0.0, dtype=torch.bfloat16):
     return out
 
 
-def gated_group_norm(y, gate, w, group, eps, gate_first, dtype=torch.bfloat16):
-    """y, gate fp32 [T, C]; groups of `group` channels; w fp32 [C] or [group] (shared by the groups)."""
+def gated_group_norm(y, gate, w, group, eps, gate_first, dtype=torch.bfloat16, gate_act="silu"):
+    """y, gate fp32 [T, C]; groups of `group` channels; w fp32 [C] or [group] (shared by the groups) or None;
+    gate_act: "silu" or "sigmoid"."""
     _cuda(y, gate, w)
     T, Cn = y.shape
     out = torch.empty(T, Cn, dtype=dtype, device=y.device)
-    _lib.lib().b200_gated_group_norm(_p(out), _p(y), Cn, _p(gate), Cn, _p(w), w.numel(), T, Cn, int(group), float(eps),
-                                     int(bool(gate_first)), _dt(dtype), _stream())
+    _lib.lib().b200_gated_group_norm(_p(out), _p(y), Cn, _p(gate), Cn, _p(w), w.numel() if w is not None else 1, T, Cn,
+                                     int(group), float(eps), int(bool(gate_first)), {"silu": 0, "sigmoid": 1}[gate_act],
+                                     _dt(dtype), _stream())
     _lib.check()
     return out
 
@@ -435,3 +437,74 @@ def moe_experts(x, h, top_idx, top_w, w_gate_up, w_down):
                                 _dt(h.dtype), _p(ws), _stream())
     _lib.check()
     return x
+
+
+def resid_add_rmsnorm(x, y, w, eps, w_offset=0.0):
+    """x fp32 [T, D] += y / rms(y) * (w_offset + w), in place."""
+    _cuda(x, y, w)
+    _lib.lib().b200_resid_add_rmsnorm(_p(x), _p(y), _p(w), x.shape[0], x.shape[1], float(eps), float(w_offset), _stream())
+    _lib.check()
+    return x
+
+
+def window_attn_prep(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, k_cache, v_cache, *, heads,
+                     rot_dims, eps):
+    """proj fp32 [T, >= heads dim + kv_heads (dim + vdim)] -> q fp32 [T, heads, dim]; writes the K / V cache rows
+    (k_cache [blocks, 64, kv_heads, dim], v_cache [blocks, 64, kv_heads, vdim])."""
+    _cuda(proj, bias, q_norm_w, k_norm_w, rot_freq, positions, slot_mapping, k_cache, v_cache)
+    T = proj.shape[0]
+    G, dk, dv = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    q = torch.empty(T, heads, dk, dtype=torch.float32, device=proj.device)
+    _lib.lib().b200_window_attn_prep(_p(proj), proj.shape[1], _p(bias), _p(q_norm_w), _p(k_norm_w), _p(rot_freq),
+                                     _p(positions), _p(slot_mapping), _p(q), _p(k_cache), _p(v_cache), T, heads, G, dk,
+                                     dv, int(rot_dims), float(eps), _dt(k_cache.dtype), _stream())
+    _lib.check()
+    return q
+
+
+def window_attn(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, block_tables, *, window, keep_first, scale,
+                softcap=0.0, split=True):
+    """q fp32 [T, heads, dim] -> [T, heads, vdim] in the cache dtype; gate fp32 [T, heads] logits or None."""
+    _cuda(q, k_cache, v_cache, sink, gate, cu_seqlens_q, context_lens, block_tables)
+    T, H, dk = q.shape
+    G, dv = k_cache.shape[2], v_cache.shape[3]
+    out = torch.empty(T, H, dv, dtype=k_cache.dtype, device=q.device)
+    nbytes = _lib.lib().b200_window_attn_workspace_bytes(T, H, G, dv, int(window), int(keep_first)) if split else 0
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
+    _lib.lib().b200_window_attn(_p(out), _p(q), _p(k_cache), _p(v_cache), _p(sink), _p(gate),
+                                gate.shape[1] if gate is not None else 0, _p(cu_seqlens_q), _p(context_lens),
+                                _p(block_tables), block_tables.shape[1], context_lens.shape[0], T, H, G, dk, dv,
+                                int(window), int(keep_first), float(scale), float(softcap), _dt(k_cache.dtype), _p(ws),
+                                _stream())
+    _lib.check()
+    return out
+
+
+def lowrank_decay(low, w2, bias, tau):
+    """low fp32 [T, rank], w2 fp32 [C, rank], bias fp32 [C] or None -> sigmoid(bias + low w2^T)^(1 / tau) fp32 [T, C]."""
+    _cuda(low, w2, bias)
+    T, C = low.shape[0], w2.shape[0]
+    out = torch.empty(T, C, dtype=torch.float32, device=low.device)
+    _lib.lib().b200_lowrank_decay(_p(out), _p(low), low.shape[1], _p(w2), _p(bias), float(tau), T, C, w2.shape[1], _stream())
+    _lib.check()
+    return out
+
+
+def decay_attn(q, k, v, state, state_slots, cu_seqlens_q, context_lens, *, head_decay=None, chan_decay=None, q_scale=1.0,
+               k_scale=1.0, act=False):
+    """q, k fp32 [T, heads, dim], v [T, heads, vdim]; head_decay fp32 [heads] or chan_decay fp32 [T, heads, dim];
+    state fp32 [slots, heads, dim, vdim] is read and updated -> o fp32 [T, heads, vdim]."""
+    T, H, dk = q.shape
+    dv = v.shape[2]
+    row = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], 1).contiguous()
+    if chan_decay is not None:
+        chan_decay = chan_decay.reshape(T, -1).contiguous()
+    _cuda(row, head_decay, chan_decay, state, state_slots, cu_seqlens_q, context_lens)
+    out = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
+    ld, e, base = row.shape[1], 4, row.data_ptr()
+    _lib.lib().b200_decay_attn(_p(out), base, base + H * dk * e, base + 2 * H * dk * e, ld, _p(head_decay),
+                               _p(chan_decay), H * dk, float(q_scale), float(k_scale), int(bool(act)), _p(state),
+                               _p(state_slots), _p(cu_seqlens_q), _p(context_lens), context_lens.shape[0], H, dk, dv,
+                               _stream())
+    _lib.check()
+    return out

@@ -30,3 +30,19 @@ def rotary_frequencies(dims: int, base: float, scaling: dict | None = None) -> t
     hi = min(math.ceil(pair_index(float(scaling["slow"]))), dims - 1)
     ramp = np.clip((idx - lo) / max(hi - lo, 0.001), 0.0, 1.0)
     return freq / s * ramp + freq * (1.0 - ramp), 0.1 * math.log(s) + 1.0
+
+
+def banded_rotary_frequencies(dims: int, base: float, scaling: dict | None = None) -> np.ndarray:
+    """Per-pair angular frequencies with scaling by wavelength band {factor s, low, high, original L}: with the
+    wavelength lam = 2 pi / f of a pair, short ones (lam < L / high) keep f, long ones (lam > L / low) get f / s, and
+    in between  f' = (1 - t) f / s + t f  with  t = (L / lam - low) / (high - low).  No magnitude factor."""
+    idx = np.arange(dims // 2, dtype=np.float64)
+    freq = np.power(float(base), -2.0 * idx / dims)
+    if not scaling:
+        return freq
+    s, low, high = float(scaling["factor"]), float(scaling["low"]), float(scaling["high"])
+    length = float(scaling["original"])
+    lam = 2.0 * math.pi / freq
+    t = (length / lam - low) / (high - low)
+    mid = (1.0 - t) * freq / s + t * freq
+    return np.where(lam < length / high, freq, np.where(lam > length / low, freq / s, mid))
