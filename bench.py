@@ -17,6 +17,10 @@ Configs (BASELINE.json `configs`):
                       fp32 residual, bf16 operands, random weights) at layer sizes that resemble a real model, next to
                       the dense fp16 LLaMA plan of equal width, depth and active feed-forward size: prefill and decode
                       tokens/s of both and the new kernels timed alone (vllm_rs_b200/bench_hybrid.py; --size, --layers).
+  zalalix             the Zalalix decoder (windowed grouped-head attention beside gated linear attention, fixed-decay
+                      linear attention layers, dense feed-forward, a norm before and after every sublayer; fp32 residual,
+                      bf16 operands, random weights) next to the Fidasun decoder of equal width and depth: prefill and
+                      decode tokens/s of both and the kernels of both timed alone (vllm_rs_b200/bench_zalalix.py).
 
 Keys of the JSON line:
   value  device-resident: step inputs already in HBM, K CUDA-graph replays of the SAME step (the same KV slot is
@@ -54,6 +58,7 @@ CONFIGS = {
                     prompt=(1536, 3584), max_tokens=128, mean_gap_steps=6.0, baseline="configs[3]",
                     label="Qwen2-72B GPTQ-int4"),
     "fidasun": dict(model="fidasun", fmt="bf16", kind="hybrid", baseline=None, label="Fidasun hybrid decoder"),
+    "zalalix": dict(model="zalalix", fmt="bf16", kind="hybrid", baseline=None, label="Zalalix decoder"),
     "l70_tp8": dict(model="llama3-70b", fmt="awq", kind="serve", gpus=8, max_num_seqs=64, requests=96,
                     prompt=(512, 2048), max_tokens=64, mean_gap_steps=1.0, baseline="configs[4]",
                     label="Llama-3-70B AWQ-int4"),
@@ -77,7 +82,7 @@ def parse():
     ap.add_argument("--no-extra-configs", action="store_true", help="N = 4 / 8: skip the q72_tp4 / l70_tp8 legs")
     ap.add_argument("--py-step", action="store_true",
                     help="e2e: drive the step from Python over the individual C symbols instead of b200_engine_step")
-    ap.add_argument("--size", default="w2048,w4096", help="--config fidasun: layer sizes, comma separated")
+    ap.add_argument("--size", default="w2048,w4096", help="--config fidasun / zalalix: layer sizes, comma separated")
     ap.add_argument("--dense-arm", action="store_true",
                     help="--config fidasun: also time the dense fp16 plan of equal size now (time-limited process)")
     ap.add_argument("--prefill-tokens", type=int, default=8192,
@@ -758,19 +763,23 @@ def run_b200(args):
         line = run_serve(args, cx, cfgname)
     elif c["kind"] == "hybrid":
         if cx.world != 1:
-            raise SystemExit("--config fidasun is a single-GPU configuration")
-        from vllm_rs_b200 import _lib, bench_hybrid
+            raise SystemExit(f"--config {cfgname} is a single-GPU configuration")
+        from vllm_rs_b200 import _lib, bench_hybrid, bench_zalalix
         launches0 = _lib.lib().b200_launch_count()
         with ClockSampler(cx.local) as clk:
-            sizes = [bench_hybrid.run(sz, layers=args.layers or 4, prefill=4096, batch=args.batch, ctx=2048,
-                                      reps=max(args.steps // 4, 3), dense=args.dense_arm)
-                     for sz in args.size.split(",")]
+            if cfgname == "zalalix":
+                sizes = [bench_zalalix.run(sz, layers=args.layers or 4, prefill=4096, batch=args.batch, ctx=2048,
+                                           reps=max(args.steps // 4, 3)) for sz in args.size.split(",")]
+            else:
+                sizes = [bench_hybrid.run(sz, layers=args.layers or 4, prefill=4096, batch=args.batch, ctx=2048,
+                                          reps=max(args.steps // 4, 3), dense=args.dense_arm)
+                         for sz in args.size.split(",")]
         first = sizes[0]
-        line = {"metric": "decode tokens/s (Fidasun hybrid decoder, random weights)",
-                "value": first["fidasun"]["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": max(args.steps // 4, 3) * 4,
-                "warmup": 3, "ms_per_step": first["fidasun"]["decode_ms"], "higher_is_better": True, "scaling": "strong",
+        line = {"metric": f"decode tokens/s ({c['label']}, random weights)",
+                "value": first[cfgname]["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": max(args.steps // 4, 3) * 4,
+                "warmup": 3, "ms_per_step": first[cfgname]["decode_ms"], "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"model": f"fidasun {first['size']} x {first['layers']} layers", "global_batch": args.batch,
+                "config": {"model": f"{cfgname} {first['size']} x {first['layers']} layers", "global_batch": args.batch,
                            "seq_len": 2048, "parallelism": "1 GPU", "l2": "weights + caches larger than L2"},
                 "clocks": clk.summary(), "gpu_launches": int(_lib.lib().b200_launch_count() - launches0),
                 "sizes": sizes}

@@ -775,7 +775,7 @@ typedef struct b200_hybrid_config {
   int32_t max_seqs, max_tokens;             /* per step */
   int32_t num_state_slots;
   float norm_eps, norm_weight_offset;       /* layer / final norms multiply by (offset + w) */
-  float embed_scale;                        /* the embedding row is multiplied by it (0 = 1) */
+  float embed_scale;                        /* the embedding row is multiplied by it */
 } b200_hybrid_config;
 
 typedef struct b200_hybrid_layer {
@@ -806,7 +806,8 @@ typedef struct b200_hybrid_layer {
   int32_t decay_rank;                       /* decay attention: > 0: per-channel decay from a low-rank projection */
   int32_t out_norm_period;                  /* decay attention: elements of out_norm_w (0: the norm has no weight);
                                                norm_groups = groups the heads x vdim outputs are normalised in */
-  float softcap, q_scale, k_scale, decay_tau, out_scale;    /* scales of 0 mean 1 */
+  float softcap, q_scale, k_scale, decay_tau;
+  float out_scale;                          /* the mixer's output is multiplied by it (every mixer; set it to 1) */
   /* w_in of the new mixers:
    *   window attention: [q: heads x dim | k: kv_heads x dim | v: kv_heads x vdim | gate: heads (if gated)]
    *   decay attention:  [q: heads x dim | k: heads x dim | v: heads x vdim | gate: heads x vdim | low: decay_rank] */

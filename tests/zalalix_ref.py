@@ -53,14 +53,14 @@ def scaled_frequencies(rot):
 
 
 def rotate(x, pos, rot):
-    """x [n]: one head's vector at position pos; pairs (2i, 2i+1) of the first rot.dims entries turn by pos * f[i]."""
+    """x [..., n]: vectors at position pos; pairs (2i, 2i+1) of the first rot.dims entries turn by pos * f[i]."""
+    f = torch.tensor(scaled_frequencies(rot), dtype=torch.float64)
+    dims = 2 * len(f)
+    c, s = torch.cos(pos * f).to(x.dtype), torch.sin(pos * f).to(x.dtype)
+    u, v = x[..., 0:dims:2], x[..., 1:dims:2]
     out = x.clone()
-    for i, f in enumerate(scaled_frequencies(rot)):
-        a = pos * f
-        c, s = math.cos(a), math.sin(a)
-        u, v = x[2 * i], x[2 * i + 1]
-        out[2 * i] = u * c - v * s
-        out[2 * i + 1] = v * c + u * s
+    out[..., 0:dims:2] = u * c - v * s
+    out[..., 1:dims:2] = v * c + u * s
     return out
 
 
@@ -77,8 +77,8 @@ def windowed_attention(h, w, m, eps):
     gate = torch.sigmoid(h @ w["g"].T)                                   # [T, H]
     rot = m.get("rot")
     if rot and rot.get("dims"):
-        q = torch.stack([torch.stack([rotate(q[t, a], t, rot) for a in range(H)]) for t in range(T)])
-        k = torch.stack([torch.stack([rotate(k[t, a], t, rot) for a in range(G)]) for t in range(T)])
+        q = torch.stack([rotate(q[t], t, rot) for t in range(T)])
+        k = torch.stack([rotate(k[t], t, rot) for t in range(T)])
     mask = m.get("mask") or {}
     size, keep = mask.get("size"), int(mask.get("keep_first", 0))
     cap = m.get("softcap")

@@ -204,7 +204,6 @@ b200_hybrid* b200_hybrid_new(const b200_hybrid_config* cfg) {
   }
   auto* r = new b200_hybrid();
   r->cfg = *cfg;
-  if (r->cfg.embed_scale == 0.f) r->cfg.embed_scale = 1.f;
   r->layers.resize(cfg->num_layers);
   r->sides.resize(cfg->num_layers);
   std::memset(r->layers.data(), 0, sizeof(b200_hybrid_layer) * cfg->num_layers);
@@ -230,12 +229,6 @@ static bool mixer_ok(const b200_hybrid_layer* l) {
            (l->decay_rank > 0 ? (l->w_decay2 && l->decay_tau > 0.f) : l->head_decay != nullptr);
   return false;
 }
-static void default_scales(b200_hybrid_layer& l) {
-  if (l.q_scale == 0.f) l.q_scale = 1.f;
-  if (l.k_scale == 0.f) l.k_scale = 1.f;
-  if (l.out_scale == 0.f) l.out_scale = 1.f;
-}
-
 void b200_hybrid_set_layer_side(b200_hybrid* r, int32_t layer, const b200_hybrid_layer* side) {
   if (layer < 0 || layer >= r->cfg.num_layers || !side) {
     set_error(1, "hybrid_set_layer_side: layer out of range");
@@ -246,7 +239,6 @@ void b200_hybrid_set_layer_side(b200_hybrid* r, int32_t layer, const b200_hybrid
     return;
   }
   r->sides[layer] = *side;
-  default_scales(r->sides[layer]);
 }
 
 void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_layer* l) {
@@ -280,7 +272,6 @@ void b200_hybrid_set_layer(b200_hybrid* r, int32_t layer, const b200_hybrid_laye
     return;
   }
   r->layers[layer] = *l;
-  default_scales(r->layers[layer]);
 }
 
 void b200_hybrid_set_globals(b200_hybrid* r, const void* embed, const void* final_norm, const void* lm_head) {

@@ -78,7 +78,7 @@ class HybridRunner:
                 self.conv_state[key] = torch.zeros(num_state_slots, max(taps - 1, 1), nconv, **f32)
                 self.rec_state[key] = torch.zeros(num_state_slots, d["heads"], rows, d["vdim"], **f32)
                 t["conv_state"], t["rec_state"] = self.conv_state[key], self.rec_state[key]
-            lw = HybridLayer(mixer=spec.mixer, **d)
+            lw = HybridLayer(mixer=spec.mixer, **{"out_scale": 1.0, "q_scale": 1.0, "k_scale": 1.0, **d})
             for name, ten in t.items():
                 if ten is None:
                     continue
