@@ -18,7 +18,8 @@
 // by the angle position * freq[i] (angles in double), writes the K and V rows at the token's slot and the query in fp32.
 //
 // Two attention kernels: an fp32 FMA form (any sizes, both dtypes; the rows of small steps split their keys over several
-// blocks and merge) and a bf16 tensor-core form for steps of many rows.
+// blocks and merge) and a bf16 tensor-core form (dim a multiple of 16, vdim of 32) whose MMA rows are token rows for
+// steps of many rows and the query heads of one key / value head for steps of few.
 #include "../../include/b200_vllm.h"
 #include <algorithm>
 #include <cstdlib>
@@ -269,15 +270,21 @@ __device__ __forceinline__ uint32_t wpack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-// NT = n-tiles (8 value columns each) per warp = vdim / 32
-template <int NT>
+// NT = n-tiles (8 value columns each) per warp = vdim / 32.  HROWS = false: the 16 MMA rows are 16 consecutive token
+// rows of one query head (prompt portions).  HROWS = true (steps of few rows, decoding): the 16 rows are the query
+// heads of ONE key / value head's group at one token -- they share the K and V rows, so one pass over the cache serves
+// them all -- and blockIdx.z owns a contiguous run of tiles of the token's visible keys (kept tokens first, then the
+// window); with nsplit > 1 the unnormalised parts go to part_o / part_ml and window_attn_merge_kernel finishes the
+// softmax (it adds the sink and the gate).
+template <int NT, bool HROWS>
 __global__ void __launch_bounds__(128)
 window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ q,
                        const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                        const float* __restrict__ sink, const float* __restrict__ gate, int ld_gate,
                        const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
                        const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_heads,
-                       int dim, int vdim, int window, int keep_first, float scale, float softcap) {
+                       int dim, int vdim, int window, int keep_first, float scale, float softcap, int nsplit,
+                       float* __restrict__ part_o, float* __restrict__ part_ml) {
   extern __shared__ __align__(16) unsigned char smraw[];
   const int P = dim + 8, PV = vdim + 8;                   // row pitches in bf16 elements (16-byte multiples)
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [WKT][P]
@@ -285,9 +292,17 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
   __nv_bfloat16* Qs = Vs + static_cast<size_t>(WKT) * PV;                   // [WQ][P]
   float* Ss = reinterpret_cast<float*>(Qs + static_cast<size_t>(WQ) * P);   // [WQ][WKT + 1]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
-  // 16 token rows of one sequence (tiles never straddle sequences)
-  int b = -1, row0 = 0, nrows = 0;
-  {
+  const int per_group = heads / kv_heads;
+  int b = -1, row0 = 0, nrows = 0, h = blockIdx.y, kvh = 0;
+  if (HROWS) {                                   // one token; heads [h, h + nrows) of key / value head kvh
+    const int rounds = (per_group + WQ - 1) / WQ;
+    row0 = blockIdx.x;
+    b = seq_of_row(cu, num_seqs, row0);
+    kvh = blockIdx.y / rounds;
+    const int first_in_group = (blockIdx.y % rounds) * WQ;
+    h = kvh * per_group + first_in_group;
+    nrows = min(WQ, per_group - first_in_group);
+  } else {                                       // 16 token rows of one sequence (tiles never straddle sequences)
     int acc = 0;
     for (int s = 0; s < num_seqs; ++s) {
       const int n = static_cast<int>(cu[s + 1] - cu[s]), tiles = (n + WQ - 1) / WQ;
@@ -301,47 +316,59 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
       acc += tiles;
     }
     if (b < 0) return;
+    kvh = h / per_group;
   }
-  const int h = blockIdx.y, kvh = h / (heads / kv_heads);
   const int pos0 = static_cast<int>(ctx[b]) - static_cast<int>(cu[b + 1] - cu[b]) + (row0 - static_cast<int>(cu[b]));
-  const int pos_last = pos0 + nrows - 1;
+  const int pos_last = HROWS ? pos0 : pos0 + nrows - 1;
   const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;        // first key of the window of the first row
   for (int e = threadIdx.x; e < WQ * dim; e += blockDim.x) {
     const int r = e / dim, d = e % dim;
-    const float v = r < nrows ? q[(static_cast<size_t>(row0 + r) * heads + h) * dim + d] : 0.f;
+    const size_t qrow = HROWS ? static_cast<size_t>(row0) * heads + h + r : static_cast<size_t>(row0 + r) * heads + h;
+    const float v = r < nrows ? q[qrow * dim + d] : 0.f;
     Qs[r * P + d] = __float2bfloat16_rn(v);
   }
   float m[2], l[2];
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
-    m[rr] = sink ? sink[h] : -1e30f;
-    l[rr] = sink ? 1.f : 0.f;
+    const int hh = HROWS ? min(h + g + rr * 8, heads - 1) : h;
+    const bool with_sink = sink && nsplit == 1;            // split runs add the sink when the parts are merged
+    m[rr] = with_sink ? sink[hh] : -1e30f;
+    l[rr] = with_sink ? 1.f : 0.f;
   }
   float o[NT][4];
 #pragma unroll
   for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   const uint32_t* bt = block_tables + static_cast<size_t>(b) * max_blocks;
-  const int rowp[2] = {pos0 + g, pos0 + g + 8};           // positions of this lane's two rows
-  // 64-aligned tiles: [0, kept_end) holds the kept tokens outside the window, [win_begin, pos_last] the window
+  const int rowp[2] = {HROWS ? pos0 : pos0 + g, HROWS ? pos0 : pos0 + g + 8};   // positions of this lane's two rows
+  // Token rows: 64-aligned tiles of positions, [0, kept_end) holds the kept tokens outside the window and
+  // [win_begin, pos_last] the window.  Head rows: tiles of the one token's visible keys, this block's run of them.
   const int win_begin = (key_lo / WKT) * WKT;
   const int kept_end = min(win_begin, ((min(max(keep_first, 0), key_lo) + WKT - 1) / WKT) * WKT);
-  for (int j0 = 0; j0 <= pos_last; j0 += WKT) {
-    if (j0 >= kept_end && j0 < win_begin) j0 = win_begin;
+  const Visible vis(pos0, window, keep_first);
+  const int ntiles = (vis.count + WKT - 1) / WKT, per = (ntiles + nsplit - 1) / nsplit;
+  const int t_first = HROWS ? static_cast<int>(blockIdx.z) * per * WKT : 0;
+  const int t_end = HROWS ? min(vis.count, t_first + per * WKT) : pos_last + 1;       // exclusive
+  for (int j0 = t_first; j0 < t_end; j0 += WKT) {
+    if (!HROWS && j0 >= kept_end && j0 < win_begin) j0 = win_begin;
     __syncthreads();
     const int kvec = dim / 8, vvec = vdim / 8;
+    // key j of tile row k (head rows: the k-th visible key of the run); rows past the run are zero
+    auto tile_key = [&](int k) { return HROWS ? vis.key(min(j0 + k, t_end - 1)) : j0 + k; };
     for (int e = threadIdx.x; e < WKT * kvec; e += blockDim.x) {
-      const int k = e / kvec, d = (e % kvec) * 8, j = j0 + k;
+      const int k = e / kvec, d = (e % kvec) * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (j <= pos_last) {
+      if (j0 + k < t_end) {
+        const int j = tile_key(k);
         const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
         v = *reinterpret_cast<const uint4*>(k_cache + (slot * kv_heads + kvh) * dim + d);
       }
       *reinterpret_cast<uint4*>(Ks + static_cast<size_t>(k) * P + d) = v;
     }
     for (int e = threadIdx.x; e < WKT * vvec; e += blockDim.x) {
-      const int k = e / vvec, d = (e % vvec) * 8, j = j0 + k;
+      const int k = e / vvec, d = (e % vvec) * 8;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (j <= pos_last) {
+      if (j0 + k < t_end) {
+        const int j = tile_key(k);
         const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
         v = *reinterpret_cast<const uint4*>(v_cache + (slot * kv_heads + kvh) * vdim + d);
       }
@@ -382,7 +409,7 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int kcol = ks * 16 + 2 * tq + (c & 1) + (c >> 1) * 8, j = j0 + kcol;
-          const bool ok = r < nrows && j <= rowp[rr] && (j >= lo || j < keep_first);
+          const bool ok = HROWS ? (r < nrows && j < t_end) : (r < nrows && j <= rowp[rr] && (j >= lo || j < keep_first));
           const float v = ok ? Ss[r * (WKT + 1) + kcol] : -1e30f;
           p[rr][ks * 4 + c] = v;
           mx[rr] = fmaxf(mx[rr], v);
@@ -437,14 +464,30 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
   for (int rr = 0; rr < 2; ++rr) {
     const int r = g + rr * 8;
     if (r >= nrows) continue;
-    float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
-    if (gate) inv *= sigmoid_f(gate[static_cast<size_t>(row0 + r) * ld_gate + h]);
-    const size_t orow = static_cast<size_t>(row0 + r) * heads + h;
+    const int hh = HROWS ? h + r : h;
+    const size_t trow = HROWS ? row0 : row0 + r;
+    const size_t orow = trow * heads + hh;
+    if (nsplit == 1) {
+      float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
+      if (gate) inv *= sigmoid_f(gate[trow * ld_gate + hh]);
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      const int d = (warp * NT + n) * 8 + 2 * tq;
-      __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
-      *reinterpret_cast<__nv_bfloat162*>(out + orow * vdim + d) = v;
+      for (int n = 0; n < NT; ++n) {
+        const int d = (warp * NT + n) * 8 + 2 * tq;
+        __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(out + orow * vdim + d) = v;
+      }
+    } else {
+      const size_t pi = orow * nsplit + blockIdx.z;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int d = (warp * NT + n) * 8 + 2 * tq;
+        part_o[pi * vdim + d] = o[n][rr * 2];
+        part_o[pi * vdim + d + 1] = o[n][rr * 2 + 1];
+      }
+      if (warp == 0 && tq == 0) {
+        part_ml[pi * 2] = m[rr];
+        part_ml[pi * 2 + 1] = l[rr];
+      }
     }
   }
 }
@@ -476,8 +519,16 @@ int window_attn_splits(int T, int heads, int kv_heads, int window, int keep_firs
   if (window > 0) n = std::min(n, (window + std::max(keep_first, 0) + 31) / 32);
   return std::max(1, std::min(n, 16));
 }
+// key splits of the heads-as-rows tensor-core form: four blocks per SM, at most one split per key tile, at most 16
+static int window_attn_mma_splits(int T, int heads, int kv_heads, int window, int keep_first) {
+  const int blocks = T * kv_heads * ((heads / kv_heads + WQ - 1) / WQ);
+  int n = (4 * sm_count() + blocks - 1) / blocks;
+  if (window > 0) n = std::min(n, (window + std::max(keep_first, 0) + WKT - 1) / WKT);
+  return std::max(1, std::min(n, 16));
+}
 size_t window_attn_workspace_bytes(int T, int heads, int kv_heads, int vdim, int window, int keep_first) {
-  const int n = window_attn_splits(T, heads, kv_heads, window, keep_first);
+  const int n = std::max(window_attn_splits(T, heads, kv_heads, window, keep_first),
+                         window_attn_mma_splits(T, heads, kv_heads, window, keep_first));
   return n == 1 ? 0 : static_cast<size_t>(T) * heads * n * (vdim + 2) * 4;
 }
 
@@ -487,19 +538,27 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
                         int dim, int vdim, int window, int keep_first, float scale, float softcap, int dt,
                         void* workspace, cudaStream_t st_) {
   if (T <= 0) return;
-  // steps of many rows in bf16: the tensor-core kernel (small steps keep the split form below)
-  if (!dt && T > 2 * sm_count() / 4 && window_mma_enabled() && window_mma_shape_ok(dim, vdim)) {
+  // bf16: the tensor-core kernel; steps of few rows take its heads-as-rows form with the keys split over blocks
+  if (!dt && window_mma_enabled() && window_mma_shape_ok(dim, vdim)) {
+    const bool hrows = T <= 2 * sm_count() / 4;
     const size_t smem = window_mma_smem(dim, vdim);
-    const dim3 grid((T + WQ - 1) / WQ + num_seqs, heads, 1);
-#define B200_WMMA(NT)                                                                                             \
+    const int nsplit = hrows && workspace ? window_attn_mma_splits(T, heads, kv_heads, window, keep_first) : 1;
+    float* part_o = reinterpret_cast<float*>(workspace);
+    float* part_ml = part_o ? part_o + static_cast<size_t>(T) * heads * nsplit * vdim : nullptr;
+    const dim3 grid = hrows ? dim3(T, kv_heads * ((heads / kv_heads + WQ - 1) / WQ), nsplit)
+                            : dim3((T + WQ - 1) / WQ + num_seqs, heads, 1);
+#define B200_WMMA2(NT, HR)                                                                                        \
   {                                                                                                                \
-    auto kern = window_attn_mma_kernel<NT>;                                                                        \
+    auto kern = window_attn_mma_kernel<NT, HR>;                                                                    \
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));               \
     kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,                          \
                                    (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,      \
                                    max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,    \
-                                   softcap);                                                                       \
+                                   softcap, nsplit, part_o, part_ml);                                              \
   }
+#define B200_WMMA(NT)                 \
+  if (hrows) B200_WMMA2(NT, true)     \
+  else B200_WMMA2(NT, false)
     bool done = true;
     switch (vdim / 32) {
       case 1: B200_WMMA(1) break;
@@ -511,8 +570,15 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
       default: done = false;
     }
 #undef B200_WMMA
+#undef B200_WMMA2
     if (done) {
       B200_CUDA_LAUNCH_CHECK();
+      if (nsplit > 1) {
+        const int th = vdim >= 256 ? 256 : (vdim >= 128 ? 128 : 64);
+        window_attn_merge_kernel<__nv_bfloat16><<<T * heads, th, 0, st_>>>((__nv_bfloat16*)out, part_o, part_ml, sink,
+                                                                           gate, ld_gate, heads, vdim, nsplit);
+        B200_CUDA_LAUNCH_CHECK();
+      }
       return;
     }
   }
