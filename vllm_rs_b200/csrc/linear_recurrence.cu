@@ -325,19 +325,34 @@ ssd_scan_kernel(float* __restrict__ out, const float* __restrict__ x, const floa
 
 // out[t, c] = sigmoid(z)^(1 / tau) with z = bias[c] + sum_r w2[c, r] * low[t, r]: the per-channel decay of gated linear
 // attention from the low-rank half of its projection.  Computed as exp(log sigmoid(z) / tau), all fp32.
-__global__ void lowrank_decay_kernel(float* __restrict__ out, const float* __restrict__ low, int ld_low,
-                                     const float* __restrict__ w2, const float* __restrict__ bias, float inv_tau, int C,
-                                     int rank) {
-  extern __shared__ float lr[];
-  const int t = blockIdx.x;
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) lr[r] = low[static_cast<size_t>(t) * ld_low + r];
+// grid = (channel blocks, token tiles): a thread owns one channel and kDecayTile tokens; the tokens' low-rank rows sit in
+// shared memory, the channel's row of w2 is read once per tile (each thread whole sectors), the stores are coalesced.
+constexpr int kDecayTile = 16;
+__global__ void __launch_bounds__(256)
+lowrank_decay_kernel(float* __restrict__ out, const float* __restrict__ low, int ld_low, const float* __restrict__ w2,
+                     const float* __restrict__ bias, float inv_tau, int T, int C, int rank) {
+  extern __shared__ float lr[];          // [kDecayTile][rank]
+  const int t0 = blockIdx.y * kDecayTile, nt = min(kDecayTile, T - t0);
+  for (int e = threadIdx.x; e < nt * rank; e += blockDim.x)
+    lr[e] = low[static_cast<size_t>(t0 + e / rank) * ld_low + e % rank];
   __syncthreads();
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float z = bias ? bias[c] : 0.f;
-    const float* w = w2 + static_cast<size_t>(c) * rank;
-    for (int r = 0; r < rank; ++r) z += w[r] * lr[r];
-    const float ls = z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
-    out[static_cast<size_t>(t) * C + c] = expf(ls * inv_tau);
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float z[kDecayTile];
+  const float b = bias ? bias[c] : 0.f;
+#pragma unroll
+  for (int i = 0; i < kDecayTile; ++i) z[i] = b;
+  const float* w = w2 + static_cast<size_t>(c) * rank;
+  for (int r = 0; r < rank; ++r) {
+    const float wv = w[r];
+#pragma unroll
+    for (int i = 0; i < kDecayTile; ++i) z[i] += wv * lr[(i < nt ? i : 0) * rank + r];
+  }
+#pragma unroll
+  for (int i = 0; i < kDecayTile; ++i) {
+    if (i >= nt) break;
+    const float ls = z[i] >= 0.f ? -log1pf(expf(-z[i])) : z[i] - log1pf(expf(z[i]));
+    out[static_cast<size_t>(t0 + i) * C + c] = expf(ls * inv_tau);
   }
 }
 
@@ -519,7 +534,13 @@ void launch_ssd_scan(float* out, const float* x, const float* Bm, const float* C
 void launch_lowrank_decay(float* out, const float* low, int ld_low, const float* w2, const float* bias, float tau, int T,
                           int C, int rank, cudaStream_t st_) {
   if (T <= 0 || C <= 0) return;
-  lowrank_decay_kernel<<<T, 256, static_cast<size_t>(rank) * 4, st_>>>(out, low, ld_low, w2, bias, 1.f / tau, C, rank);
+  if (rank <= 0 || rank > 512) {
+    set_error(1, "lowrank_decay: the rank must be between 1 and 512");
+    return;
+  }
+  const dim3 grid((C + 255) / 256, (T + kDecayTile - 1) / kDecayTile);
+  lowrank_decay_kernel<<<grid, 256, static_cast<size_t>(kDecayTile) * rank * 4, st_>>>(out, low, ld_low, w2, bias,
+                                                                                       1.f / tau, T, C, rank);
   B200_CUDA_LAUNCH_CHECK();
 }
 
@@ -585,7 +606,7 @@ void b200_ssd_scan(float* out, const float* x, const float* Bm, const float* Cm,
 }
 void b200_lowrank_decay(float* out, const float* low, int32_t ld_low, const float* w2, const float* bias, float tau,
                          int32_t num_tokens, int32_t channels, int32_t rank, int64_t stream) {
-  B200_CHECK_ARG(out && low && w2 && tau > 0.f && channels > 0 && rank > 0 && rank <= 8192, "lowrank_decay: bad arguments");
+  B200_CHECK_ARG(out && low && w2 && tau > 0.f && channels > 0 && rank > 0 && rank <= 512, "lowrank_decay: bad arguments (rank up to 512)");
   b200::launch_lowrank_decay(out, low, ld_low, w2, bias, tau, num_tokens, channels, rank,
                              reinterpret_cast<cudaStream_t>(stream));
 }

@@ -18,8 +18,9 @@
 // by the angle position * freq[i] (angles in double), writes the K and V rows at the token's slot and the query in fp32.
 //
 // Two attention kernels: an fp32 FMA form (any sizes, both dtypes; the rows of small steps split their keys over several
-// blocks and merge) and a bf16 tensor-core form (dim a multiple of 16, vdim of 32) whose MMA rows are token rows for
-// steps of many rows and the query heads of one key / value head for steps of few.
+// blocks and merge) and bf16 tensor-core forms: for steps of many rows 64 token rows per block with the softmax in the
+// accumulator registers (dim and vdim multiples of 16, vdim up to 128; otherwise 16 rows per block, vdim a multiple of
+// 32), for steps of few rows the query heads of one key / value head as the MMA rows with the keys split over blocks.
 #include "../../include/b200_vllm.h"
 #include <algorithm>
 #include <cstdlib>
@@ -492,10 +493,207 @@ window_attn_mma_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict_
   }
 }
 
+
+// ---- token rows, second form (value sizes up to 128): block = 4 warps = one query head x 64 consecutive token rows of
+// ONE sequence, every warp owning 16 rows outright.  A warp computes the scores of its rows against all 64 keys of a
+// tile (8 n-tiles of fp32 accumulators, K fragments by ldmatrix), runs the fp32 online softmax on them in registers --
+// the score accumulators ARE the A fragments of P, so nothing passes through shared memory and no warp repeats
+// another's exponentials -- and multiplies P (bf16) with all value columns (V fragments by ldmatrix.trans).  The K / V
+// tile in shared memory serves four times as many rows as in the form above.  Tiles as there: 64-aligned runs of
+// positions, first those that hold kept tokens outside the window, then the window of the block's rows.
+constexpr int RQ = 64;
+template <int NTV>                   // n-tiles of 8 value columns = vdim / 8
+__global__ void __launch_bounds__(128)
+window_attn_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ q,
+                        const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                        const float* __restrict__ sink, const float* __restrict__ gate, int ld_gate,
+                        const uint32_t* __restrict__ cu, const uint32_t* __restrict__ ctx,
+                        const uint32_t* __restrict__ block_tables, int max_blocks, int num_seqs, int heads, int kv_heads,
+                        int dim, int vdim, int window, int keep_first, float scale, float softcap) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int P = dim + 8, PV = vdim + 8;
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smraw);              // [WKT][P]
+  __nv_bfloat16* Vs = Ks + static_cast<size_t>(WKT) * P;                    // [WKT][PV]
+  __nv_bfloat16* Qs = Vs + static_cast<size_t>(WKT) * PV;                   // [RQ][P]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+  int b = -1, row0 = 0, nrows = 0;
+  {
+    int acc = 0;
+    for (int s = 0; s < num_seqs; ++s) {
+      const int n = static_cast<int>(cu[s + 1] - cu[s]), tiles = (n + RQ - 1) / RQ;
+      if (static_cast<int>(blockIdx.x) < acc + tiles) {
+        const int k = blockIdx.x - acc;
+        b = s;
+        row0 = cu[s] + k * RQ;
+        nrows = min(RQ, n - k * RQ);
+        break;
+      }
+      acc += tiles;
+    }
+    if (b < 0) return;
+  }
+  const int h = blockIdx.y, kvh = h / (heads / kv_heads);
+  const int pos0 = static_cast<int>(ctx[b]) - static_cast<int>(cu[b + 1] - cu[b]) + (row0 - static_cast<int>(cu[b]));
+  const int pos_last = pos0 + nrows - 1;
+  const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  for (int e = threadIdx.x; e < RQ * dim; e += blockDim.x) {
+    const int r = e / dim, d = e % dim;
+    const float v = r < nrows ? q[(static_cast<size_t>(row0 + r) * heads + h) * dim + d] : 0.f;
+    Qs[r * P + d] = __float2bfloat16_rn(v);
+  }
+  const int wr = warp * 16;                                // this warp's first row within the block
+  const int rowi[2] = {wr + g, wr + g + 8};
+  const int rowp[2] = {pos0 + rowi[0], pos0 + rowi[1]};
+  float m[2], l[2];
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    m[rr] = sink ? sink[h] : -1e30f;
+    l[rr] = sink ? 1.f : 0.f;
+  }
+  float o[NTV][4];
+#pragma unroll
+  for (int n = 0; n < NTV; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  const uint32_t* bt = block_tables + static_cast<size_t>(b) * max_blocks;
+  const int win_begin = (key_lo / WKT) * WKT;
+  const int kept_end = min(win_begin, ((min(max(keep_first, 0), key_lo) + WKT - 1) / WKT) * WKT);
+  const int kvec = dim / 8, vvec = vdim / 8;
+  for (int j0 = 0; j0 <= pos_last; j0 += WKT) {
+    if (j0 >= kept_end && j0 < win_begin) j0 = win_begin;
+    __syncthreads();
+    for (int e = threadIdx.x; e < WKT * kvec; e += blockDim.x) {
+      const int k = e / kvec, d = (e % kvec) * 8, j = j0 + k;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j <= pos_last) {
+        const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
+        v = *reinterpret_cast<const uint4*>(k_cache + (slot * kv_heads + kvh) * dim + d);
+      }
+      *reinterpret_cast<uint4*>(Ks + static_cast<size_t>(k) * P + d) = v;
+    }
+    for (int e = threadIdx.x; e < WKT * vvec; e += blockDim.x) {
+      const int k = e / vvec, d = (e % vvec) * 8, j = j0 + k;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j <= pos_last) {
+        const size_t slot = static_cast<size_t>(bt[j / kPage]) * kPage + (j % kPage);
+        v = *reinterpret_cast<const uint4*>(v_cache + (slot * kv_heads + kvh) * vdim + d);
+      }
+      *reinterpret_cast<uint4*>(Vs + static_cast<size_t>(k) * PV + d) = v;
+    }
+    __syncthreads();
+    // this warp's rows see nothing of the tile: every key is later than its last row, or the tile lies wholly between
+    // the kept tokens and the window of its first row
+    const int w_first = pos0 + wr, w_last = min(pos0 + wr + 15, pos_last);
+    const int w_lo = window > 0 ? max(0, w_first - window + 1) : 0;
+    if (wr >= nrows || j0 > w_last || (j0 + WKT <= w_lo && j0 >= keep_first)) continue;
+    float sc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+    for (int kk = 0; kk < dim; kk += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(Qs + rowi[0] * P + kk + 2 * tq);
+      a[1] = *reinterpret_cast<const uint32_t*>(Qs + rowi[1] * P + kk + 2 * tq);
+      a[2] = *reinterpret_cast<const uint32_t*>(Qs + rowi[0] * P + kk + 2 * tq + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(Qs + rowi[1] * P + kk + 2 * tq + 8);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {        // n-tiles 2 np, 2 np + 1: matrices (tile, k half) = lane >> 3
+        const int mi = lane >> 3;
+        const __nv_bfloat16* src = Ks + static_cast<size_t>((2 * np + (mi >> 1)) * 8 + (lane & 7)) * P + kk + (mi & 1) * 8;
+        uint32_t r0, r1, r2, r3;
+        const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(src));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+        wmma_bf16_16816(sc[2 * np], a, r0, r1);
+        wmma_bf16_16816(sc[2 * np + 1], a, r2, r3);
+      }
+    }
+    // scale, cap, mask; row maxima over the lane's entries and the quad
+    float mx[2] = {-1e30f, -1e30f};
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const int lo = window > 0 ? max(0, rowp[rr] - window + 1) : 0;
+#pragma unroll
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int j = j0 + n * 8 + 2 * tq + c;
+          const bool ok = rowi[rr] < nrows && j <= rowp[rr] && (j >= lo || j < keep_first);
+          const float v = ok ? cap_score(sc[n][rr * 2 + c] * scale, softcap) : -1e30f;
+          sc[n][rr * 2 + c] = v;
+          mx[rr] = fmaxf(mx[rr], v);
+        }
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+      mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+    }
+    float alpha[2];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      const float mn = fmaxf(m[rr], mx[rr]);
+      alpha[rr] = expf(m[rr] - mn);
+      float sum = 0.f;
+#pragma unroll
+      for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const float v = sc[n][rr * 2 + c];
+          const float e = v > -1e29f ? expf(v - mn) : 0.f;
+          sc[n][rr * 2 + c] = e;
+          sum += e;
+        }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l[rr] = l[rr] * alpha[rr] + sum;
+      m[rr] = mn;
+    }
+#pragma unroll
+    for (int n = 0; n < NTV; ++n) {
+      o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+    }
+    // O += P V: per 16 keys the A fragments are two neighbouring score tiles
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      uint32_t a[4];
+      a[0] = wpack_bf16(sc[2 * ks][0], sc[2 * ks][1]);
+      a[1] = wpack_bf16(sc[2 * ks][2], sc[2 * ks][3]);
+      a[2] = wpack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
+      a[3] = wpack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+#pragma unroll
+      for (int n = 0; n < NTV; n += 2) {
+        const __nv_bfloat16* src = Vs + static_cast<size_t>(ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * PV + n * 8 + (lane >> 4) * 8;
+        uint32_t r0, r1, r2, r3;
+        const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(src));
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+        wmma_bf16_16816(o[n], a, r0, r1);
+        wmma_bf16_16816(o[n + 1], a, r2, r3);
+      }
+    }
+  }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    if (rowi[rr] >= nrows) continue;
+    const size_t trow = static_cast<size_t>(row0 + rowi[rr]);
+    float inv = l[rr] > 0.f ? 1.f / l[rr] : 0.f;
+    if (gate) inv *= sigmoid_f(gate[trow * ld_gate + h]);
+#pragma unroll
+    for (int n = 0; n < NTV; ++n) {
+      const int d = n * 8 + 2 * tq;
+      __nv_bfloat162 v = __floats2bfloat162_rn(o[n][rr * 2] * inv, o[n][rr * 2 + 1] * inv);
+      *reinterpret_cast<__nv_bfloat162*>(out + (trow * heads + h) * vdim + d) = v;
+    }
+  }
+}
+
 static bool window_mma_enabled() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("B200_WINDOW_MMA");       // 0: the FMA kernel for every step (A/B arm)
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+static bool window_rows_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("B200_WINDOW_ROWS");      // 0: token rows take the 16-row form (A/B arm)
     v = (e && e[0] == '0') ? 0 : 1;
   }
   return v == 1;
@@ -538,6 +736,38 @@ void launch_window_attn(void* out, const float* q, const void* k_cache, const vo
                         int dim, int vdim, int window, int keep_first, float scale, float softcap, int dt,
                         void* workspace, cudaStream_t st_) {
   if (T <= 0) return;
+  // bf16, steps of many rows, value sizes up to 128: the tensor-core form with 64 token rows per block
+  if (!dt && window_mma_enabled() && T > 2 * sm_count() / 4 && window_rows_enabled() && dim % 16 == 0 && vdim % 16 == 0 &&
+      vdim <= 128) {
+    const size_t smem = (static_cast<size_t>(WKT + RQ) * (dim + 8) + static_cast<size_t>(WKT) * (vdim + 8)) * 2;
+    const dim3 grid((T + RQ - 1) / RQ + num_seqs, heads, 1);
+#define B200_WROWS(NTV)                                                                                           \
+  {                                                                                                                \
+    auto kern = window_attn_rows_kernel<NTV>;                                                                      \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));               \
+    kern<<<grid, 128, smem, st_>>>((__nv_bfloat16*)out, q, (const __nv_bfloat16*)k_cache,                          \
+                                   (const __nv_bfloat16*)v_cache, sink, gate, ld_gate, cu, ctx, block_tables,      \
+                                   max_blocks, num_seqs, heads, kv_heads, dim, vdim, window, keep_first, scale,    \
+                                   softcap);                                                                       \
+  }
+    bool done = smem <= 200 * 1024;
+    if (done) switch (vdim / 8) {
+      case 2: B200_WROWS(2) break;
+      case 4: B200_WROWS(4) break;
+      case 6: B200_WROWS(6) break;
+      case 8: B200_WROWS(8) break;
+      case 10: B200_WROWS(10) break;
+      case 12: B200_WROWS(12) break;
+      case 14: B200_WROWS(14) break;
+      case 16: B200_WROWS(16) break;
+      default: done = false;
+    }
+#undef B200_WROWS
+    if (done) {
+      B200_CUDA_LAUNCH_CHECK();
+      return;
+    }
+  }
   // bf16: the tensor-core kernel; steps of few rows take its heads-as-rows form with the keys split over blocks
   if (!dt && window_mma_enabled() && window_mma_shape_ok(dim, vdim)) {
     const bool hrows = T <= 2 * sm_count() / 4;
