@@ -101,6 +101,11 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
                : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async16(float* smem, const float* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
+               "l"(gmem)
+               : "memory");
+}
 template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
@@ -356,10 +361,14 @@ lowrank_decay_kernel(float* __restrict__ out, const float* __restrict__ low, int
   }
 }
 
-// tokens per pass of the decayed-state scan: with a per-channel decay a third row set is staged, so half as many
-constexpr int decay_chunk_for(int rows, bool chan) { return chan ? (chunk_for(rows) > 16 ? 16 : chunk_for(rows) / 2) : chunk_for(rows); }
+// tokens per pass of the decayed-state scan (two buffers of this many; a per-channel decay stages a third row set)
+constexpr int decay_chunk_for(int rows, bool chan) { return (chan ? 8 : 16) / (rows > 128 ? 2 : 1); }
+constexpr int kDecayPad = 4;       // floats between the row segments of two lanes: 16-byte loads without bank conflicts
 
-// grid = (column blocks, heads, sequences); block = 128 threads = 16 columns x kRowSplit lanes, as the scans above.
+// grid = (column blocks, heads, sequences); block = 128 threads = 16 columns x kRowSplit lanes.  Unlike the scans above
+// a lane holds NR = DK / 8 CONSECUTIVE rows of its column (rows part * NR ..), and a token's k / q / decay rows lie in
+// shared memory as eight padded segments, so a lane reads its segment with 16-byte loads; four tokens are walked per
+// round so that their read-out reductions (shuffles) overlap the next tokens' state updates.
 // CHAN: the decay is per key channel and token (chan_decay [T, heads, dim], row stride ld_decay); otherwise one
 // constant per head (head_decay [heads]).
 template <int DK, bool CHAN>
@@ -369,9 +378,10 @@ decay_attn_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
                   const float* __restrict__ chan_decay, int ld_decay, float q_scale, float k_scale, int act,
                   float* __restrict__ state, const int32_t* __restrict__ slots, const uint32_t* __restrict__ cu,
                   const uint32_t* __restrict__ ctx, int heads, int dim, int vdim) {
-  constexpr int RS = kRowSplit, NR = DK / RS, kChunk = decay_chunk_for(DK, CHAN);
-  __shared__ float ks[2][kChunk][DK], qs[2][kChunk][DK], as[CHAN ? 2 : 1][CHAN ? kChunk : 1][CHAN ? DK : 1],
-      vs[2][kChunk][kScanCols];
+  constexpr int RS = kRowSplit, NR = DK / RS, SEG = NR + kDecayPad, DKP = RS * SEG, kChunk = decay_chunk_for(DK, CHAN);
+  constexpr int UN = 4;              // tokens per round of the walk
+  __shared__ __align__(16) float ks[2][kChunk][DKP], qs[2][kChunk][DKP],
+      as[CHAN ? 2 : 1][CHAN ? kChunk : 1][CHAN ? DKP : 4], vs[2][kChunk][kScanCols];
   const int h = blockIdx.y, b = blockIdx.z;
   const int part = threadIdx.x % RS;
   const int col = blockIdx.x * (blockDim.x / RS) + threadIdx.x / RS;
@@ -383,30 +393,58 @@ decay_attn_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
   float s[NR];
 #pragma unroll
   for (int j = 0; j < NR; ++j) {
-    const int i = j * RS + part;
+    const int i = part * NR + j;
     s[j] = (!fresh && live && i < dim) ? sp[static_cast<size_t>(i) * vdim] : 0.f;
   }
   const float hd = CHAN ? 0.f : head_decay[h];
-  if (dim < DK) {                                                         // the padding past `dim` stays zero
-    for (int e = threadIdx.x; e < 2 * kChunk * DK; e += kScanThreads) (&ks[0][0][0])[e] = (&qs[0][0][0])[e] = 0.f;
-    if (CHAN)
-      for (int e = threadIdx.x; e < 2 * kChunk * DK; e += kScanThreads) (&as[0][0][0])[e] = 0.f;
-  }
+  if (dim < DK)                          // rows past `dim` stay zero (the padding between segments is never read)
+    for (int e = threadIdx.x; e < 2 * kChunk * DKP; e += kScanThreads) {
+      (&ks[0][0][0])[e] = (&qs[0][0][0])[e] = 0.f;
+      if (CHAN) (&as[0][0][0])[e] = 0.f;
+    }
   for (int e = threadIdx.x; e < 2 * kChunk * kScanCols; e += kScanThreads) (&vs[0][0][0])[e] = 0.f;
   __syncthreads();
+  auto at = [](int i) { return i + (i / NR) * kDecayPad; };       // place of row i in a padded token row
+  // 16-byte copies where four consecutive rows share a segment and every source address is 16-byte aligned
+  const bool wide = NR % 4 == 0 && dim % 4 == 0 && ld % 4 == 0 && (!CHAN || ld_decay % 4 == 0) &&
+                    ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                      (CHAN ? reinterpret_cast<uintptr_t>(chan_decay) : 0)) & 15) == 0;
   auto fetch = [&](int c0, int buf) {
     const int n = min(kChunk, t1 - c0);
-    for (int e = threadIdx.x; e < n * dim; e += kScanThreads) {
-      const int r = e / dim, i = e - r * dim;
-      cp_async4(&ks[buf][r][i], k + static_cast<size_t>(c0 + r) * ld + h * dim + i);
-      cp_async4(&qs[buf][r][i], q + static_cast<size_t>(c0 + r) * ld + h * dim + i);
-      if (CHAN) cp_async4(&as[buf][r][i], chan_decay + static_cast<size_t>(c0 + r) * ld_decay + h * dim + i);
+    if (wide) {
+      const int d4 = dim / 4;
+      for (int e = threadIdx.x; e < n * d4; e += kScanThreads) {
+        const int r = e / d4, i = (e - r * d4) * 4;
+        cp_async16(&ks[buf][r][at(i)], k + static_cast<size_t>(c0 + r) * ld + h * dim + i);
+        cp_async16(&qs[buf][r][at(i)], q + static_cast<size_t>(c0 + r) * ld + h * dim + i);
+        if (CHAN) cp_async16(&as[buf][r][at(i)], chan_decay + static_cast<size_t>(c0 + r) * ld_decay + h * dim + i);
+      }
+    } else {
+      for (int e = threadIdx.x; e < n * dim; e += kScanThreads) {
+        const int r = e / dim, i = e - r * dim;
+        cp_async4(&ks[buf][r][at(i)], k + static_cast<size_t>(c0 + r) * ld + h * dim + i);
+        cp_async4(&qs[buf][r][at(i)], q + static_cast<size_t>(c0 + r) * ld + h * dim + i);
+        if (CHAN) cp_async4(&as[buf][r][at(i)], chan_decay + static_cast<size_t>(c0 + r) * ld_decay + h * dim + i);
+      }
     }
     for (int e = threadIdx.x; e < n * kScanCols; e += kScanThreads) {
       const int r = e / kScanCols, c = blockIdx.x * kScanCols + e % kScanCols;
       if (c < vdim) cp_async4(&vs[buf][r][e % kScanCols], v + static_cast<size_t>(c0 + r) * ld + h * vdim + c);
     }
     cp_async_commit();
+  };
+  // NR floats of a lane's segment: 16-byte loads where the segment is a whole number of them
+  auto load_seg = [&](float* dst, const float* src) {
+    if constexpr (NR % 4 == 0) {
+#pragma unroll
+      for (int j = 0; j < NR; j += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(src + j);
+        dst[j] = x.x; dst[j + 1] = x.y; dst[j + 2] = x.z; dst[j + 3] = x.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < NR; ++j) dst[j] = src[j];
+    }
   };
   fetch(t0, 0);
   int buf = 0;
@@ -420,39 +458,56 @@ decay_attn_kernel(float* __restrict__ out, const float* __restrict__ q, const fl
     }
     __syncthreads();
     // activation and scales of the pass, in place
-    for (int e = threadIdx.x; e < n * dim; e += kScanThreads) {
-      const int r = e / dim, i = e - r * dim;
-      const float kv = ks[buf][r][i], qv = qs[buf][r][i];
-      ks[buf][r][i] = (act ? silu_exact(kv) : kv) * k_scale;
-      qs[buf][r][i] = (act ? silu_exact(qv) : qv) * q_scale;
+    if (act || q_scale != 1.f || k_scale != 1.f) {
+      for (int e = threadIdx.x; e < n * dim; e += kScanThreads) {
+        const int r = e / dim, i = at(e - r * dim);
+        const float kv = ks[buf][r][i], qv = qs[buf][r][i];
+        ks[buf][r][i] = (act ? silu_exact(kv) : kv) * k_scale;
+        qs[buf][r][i] = (act ? silu_exact(qv) : qv) * q_scale;
+      }
+      if (act)
+        for (int e = threadIdx.x; e < n * kScanCols; e += kScanThreads)
+          vs[buf][e / kScanCols][e % kScanCols] = silu_exact(vs[buf][e / kScanCols][e % kScanCols]);
+      __syncthreads();
     }
-    if (act)
-      for (int e = threadIdx.x; e < n * kScanCols; e += kScanThreads)
-        vs[buf][e / kScanCols][e % kScanCols] = silu_exact(vs[buf][e / kScanCols][e % kScanCols]);
-    __syncthreads();
-    for (int r = 0; r < n; ++r) {
-      const float vv = vs[buf][r][threadIdx.x / RS];
-      float y0 = 0.f, y1 = 0.f;
+    for (int r = 0; r < n; r += UN) {      // n is the same in every thread: the guards below do not diverge
+      float y[UN];
 #pragma unroll
-      for (int j = 0; j < NR; j += 2) {
-        s[j] = (CHAN ? as[buf][r][j * RS + part] : hd) * s[j] + ks[buf][r][j * RS + part] * vv;
-        y0 += qs[buf][r][j * RS + part] * s[j];
-        if (j + 1 < NR) {
-          s[j + 1] = (CHAN ? as[buf][r][(j + 1) * RS + part] : hd) * s[j + 1] + ks[buf][r][(j + 1) * RS + part] * vv;
-          y1 += qs[buf][r][(j + 1) * RS + part] * s[j + 1];
+      for (int u = 0; u < UN; ++u) {
+        y[u] = 0.f;
+        if (r + u < n) {
+          float kr[NR], qr[NR], ar[CHAN ? NR : 1];
+          load_seg(kr, &ks[buf][r + u][part * SEG]);
+          load_seg(qr, &qs[buf][r + u][part * SEG]);
+          if (CHAN) load_seg(ar, &as[buf][r + u][part * SEG]);
+          const float vv = vs[buf][r + u][threadIdx.x / RS];
+          float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+          for (int j = 0; j < NR; j += 2) {
+            s[j] = (CHAN ? ar[j] : hd) * s[j] + kr[j] * vv;
+            y0 += qr[j] * s[j];
+            if (j + 1 < NR) {
+              s[j + 1] = (CHAN ? ar[CHAN ? j + 1 : 0] : hd) * s[j + 1] + kr[j + 1] * vv;
+              y1 += qr[j + 1] * s[j + 1];
+            }
+          }
+          y[u] = y0 + y1;
         }
       }
-      float y = y0 + y1;
 #pragma unroll
-      for (int o = 1; o < RS; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-      if (live && part == 0) out[(static_cast<size_t>(c0 + r) * heads + h) * vdim + col] = y;
+      for (int o = 1; o < RS; o <<= 1)
+#pragma unroll
+        for (int u = 0; u < UN; ++u) y[u] += __shfl_xor_sync(0xffffffffu, y[u], o);
+#pragma unroll
+      for (int u = 0; u < UN; ++u)           // lane `u` of the column stores token r + u
+        if (live && part == u && r + u < n) out[(static_cast<size_t>(c0 + r + u) * heads + h) * vdim + col] = y[u];
     }
     __syncthreads();                       // this buffer is refilled by the next pass's fetch
   }
   if (live) {
 #pragma unroll
     for (int j = 0; j < NR; ++j) {
-      const int i = j * RS + part;
+      const int i = part * NR + j;
       if (i < dim) sp[static_cast<size_t>(i) * vdim] = s[j];
     }
   }
