@@ -144,7 +144,7 @@ def _plain_window_attention(q, k, v, gate, rows_pos, window, keep, scale, cap, s
 @pytest.mark.parametrize("window,keep", [(0, 0), (5, 0), (5, 3), (64, 64), (64, 1), (70, 3), (130, 70), (1, 0)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("split", [True, False])
-@pytest.mark.parametrize("dk,dv,H,G", [(12, 20, 4, 2), (32, 64, 3, 1), (16, 160, 2, 1)])   # the last two: tensor-core forms
+@pytest.mark.parametrize("dk,dv,H,G", [(12, 20, 4, 2), (32, 64, 3, 1), (16, 160, 2, 1), (16, 32, 34, 2)])   # the last three: tensor-core forms (the last: a group wider than 16 heads)
 def test_window_attention_sees_exactly_its_window_and_kept_tokens(lib, window, keep, dtype, split, dk, dv, H, G):
     """Keys carry a position tag u and its square, so a query can put a sharp peak on any position.  Four queries per
     row: a ramp that prefers the earliest visible key, a ramp that prefers the latest, a peak on the key JUST OUTSIDE

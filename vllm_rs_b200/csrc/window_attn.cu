@@ -6,10 +6,10 @@
 //   k_cache [num_blocks, 64, kv_heads, dim]    v_cache [num_blocks, 64, kv_heads, vdim]    (bf16 or fp32)
 // Query head h reads key / value head h / (heads / kv_heads).  Options, each a parameter:
 //   * sliding window that keeps the first tokens: position i sees j <= i with i - j < window or j < keep_first
-//     (window <= 0: every j <= i); kept tokens keep their own positions
+//     (window <= 0: every j <= i); nothing is re-numbered: rotary angles and distances use the true positions
 //   * capped scores: s <- cap * tanh(s / cap)  (cap <= 0: off), applied after the scale
-//   * a per-head sink logit that joins the softmax denominator without a key or value (NULL: none); a logit of 0 is
-//     "one added to the denominator"
+//   * a per-head sink logit that joins the softmax denominator without a key or value (NULL: none); a logit of 0
+//     contributes exp(0) = 1, i.e. p_j = e^(s_j) / (1 + sum_k e^(s_k))
 //   * a per-head output gate: the head's output is multiplied by sigmoid(gate[t, h]) (NULL: none)
 //
 // window_attn_prep_kernel: from the fused projection row [q (heads x dim) | k (kv_heads x dim) | v (kv_heads x vdim) | ...]

@@ -78,7 +78,7 @@ def build(cfg, tensors, *, dtype=torch.bfloat16, device="cuda", num_blocks, max_
         t.update(w_in=mat(p + "q", p + "k", p + "v", p + "g"), w_o=mat(p + "o"),
                  in_bias=vec(p + "q.b", p + "k.b", p + "v.b"), o_bias=vec(p + "o.b"),
                  q_norm_w=vec(p + "q.norm"), k_norm_w=vec(p + "k.norm"),
-                 sink=torch.zeros(H, dtype=torch.float32, device=dev))       # one added to the softmax denominator
+                 sink=torch.zeros(H, dtype=torch.float32, device=dev))       # sink logit 0: a unit term in the softmax denominator
         return LayerSpec(MIXER_WINDOW_ATTN, d, t)
 
     specs = []
