@@ -144,8 +144,18 @@ def _plain_window_attention(q, k, v, gate, rows_pos, window, keep, scale, cap, s
 @pytest.mark.parametrize("window,keep", [(0, 0), (5, 0), (5, 3), (64, 64), (64, 1), (70, 3), (130, 70), (1, 0)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("split", [True, False])
-@pytest.mark.parametrize("dk,dv,H,G", [(12, 20, 4, 2), (32, 64, 3, 1), (16, 160, 2, 1), (16, 32, 34, 2)])   # the last three: tensor-core forms (the last: a group wider than 16 heads)
+@pytest.mark.parametrize("dk,dv,H,G", [(12, 20, 4, 2), (32, 64, 3, 1), (16, 160, 2, 1)])   # the last two: tensor-core forms
 def test_window_attention_sees_exactly_its_window_and_kept_tokens(lib, window, keep, dtype, split, dk, dv, H, G):
+    _check_window_attention(window, keep, dtype, split, dk, dv, H, G)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_window_attention_with_a_group_wider_than_a_tile(lib, dtype):
+    """17 query heads per key / value head: more than the 16 rows of an MMA tile and than the warps of a block."""
+    _check_window_attention(70, 3, dtype, True, 16, 32, 34, 2, row_sets=([199], [64], list(range(100, 200))))
+
+
+def _check_window_attention(window, keep, dtype, split, dk, dv, H, G, row_sets=None):
     """Keys carry a position tag u and its square, so a query can put a sharp peak on any position.  Four queries per
     row: a ramp that prefers the earliest visible key, a ramp that prefers the latest, a peak on the key JUST OUTSIDE
     the window's far edge, and a peak on the first key that is NOT kept: had the kernel seen a key one place beyond an
@@ -167,8 +177,8 @@ def test_window_attention_sees_exactly_its_window_and_kept_tokens(lib, window, k
     bt = _i32([pages])
     tol = 2e-3 if dtype == torch.float32 else 4e-2
     sharp = 16384.0
-    for rows_pos in ([199], [64], [63], [0], list(range(100, 200)), list(range(120, 200)), list(range(0, 70)),
-                     list(range(0, 129))):
+    for rows_pos in row_sets or ([199], [64], [63], [0], list(range(100, 200)), list(range(120, 200)), list(range(0, 70)),
+                                 list(range(0, 129))):
         T = len(rows_pos)
         pos = torch.tensor(rows_pos, dtype=torch.float32)
         for form, cap, sink in (("early", 0.0, False), ("early", 300.0, True), ("late", 0.0, True), ("window", 0.0, False),
